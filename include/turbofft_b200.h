@@ -1,0 +1,134 @@
+/* turbofft_b200 -- C ABI of the B200 (sm_100a) batched power-of-two C2C FFT with
+ * fused two-sided ABFT checksums.
+ *
+ * The reference (shixun404/TurboFFT) has no library API: its "operator" is the
+ * kernel-pointer table TurboFFT_Kernel_Entry<T, if_ft, if_err, gpu>::turboFFTArr
+ * (include/TurboFFT.h:22-25), driven by the launch protocol of test_turbofft()
+ * (main.cu:4-73).  Each entry point below names the piece of that protocol it
+ * replaces.  All pointers are plain device or host addresses; no C++ or torch
+ * types cross this boundary.  Every function returns 0 on success or a negative
+ * tfft_status; nothing calls exit().
+ *
+ * Conventions: forward transform, unnormalised, exp(-2*pi*i*n*k/N)
+ * (include/utils/initializeData.h:31-37); input and output are [batch][N]
+ * interleaved complex (float2 or double2) in natural order; the input buffer is
+ * never written unless in == out.
+ */
+#ifndef TURBOFFT_B200_H
+#define TURBOFFT_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tfft_plan_s* tfft_plan;
+
+typedef enum {
+    TFFT_OK = 0,
+    TFFT_ERR_BAD_ARG = -1,      /* null pointer, logN out of range, batch < 1, ... */
+    TFFT_ERR_UNSUPPORTED = -2,  /* no parameter row / no compiled kernel for this size */
+    TFFT_ERR_CUDA = -3,         /* a CUDA call failed; see tfft_last_cuda_error() */
+    TFFT_ERR_PARAM_FILE = -4,   /* parameter CSV missing or malformed */
+    TFFT_ERR_ALLOC = -5,        /* device or host allocation failed */
+    TFFT_ERR_TOO_LARGE = -6     /* size beyond a stated maximum */
+} tfft_status;
+
+/* dtype codes follow the reference CLI: --datatype 0 = float2, 1 = double2
+ * (include/utils/CommandLineParser.h:67-69). */
+enum { TFFT_FLOAT2 = 0, TFFT_DOUBLE2 = 1 };
+
+/* Replaces: load_parameters() + the geometry loop of test_turbofft()
+ * (include/utils/readCSV.h:13-33, main.cu:8-41) and the table set-up of
+ * TurboFFT_main()/initializeData() (main.cu:85-93, initializeData.h:31-37).
+ * param_csv: path of an 11-column parameter file (logN, launches, logN1..3,
+ * BS1..3, n1..3; readme.md:46-60) or NULL for the built-in B200 table.
+ * if_ft / if_err / thread_bs: the reference CLI flags of the same names.
+ * Allocates the twiddle and checksum tables, the scratch buffer of multi-launch
+ * plans and the FT status buffers on `device`. */
+int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int if_ft, int if_err,
+                     int thread_bs, const char* param_csv, int device);
+
+/* Replaces: the launch loop of test_turbofft() (main.cu:53-62) without its
+ * per-launch cudaDeviceSynchronize().  `in` and `out` are device pointers to
+ * batch*N complex elements; the result is always at `out` (the reference leaves
+ * it in a launch-count dependent half of a 2x buffer, main.cu:11-12,72).
+ * in == out is allowed except for 1-launch plans with if_err (the located tile
+ * is recomputed from the input).  `stream` is a cudaStream_t (NULL = default).
+ * Stream ordered; returns without synchronising. */
+int tfft_exec(tfft_plan plan, const void* in, void* out, void* stream);
+
+/* Same transform with HOST buffers: copies batch*N elements to the device, runs
+ * tfft_exec and copies the result back, then synchronises.  Replaces the
+ * cudaMemcpy pair around the launches in initializeData()/test_turbofft()
+ * (initializeData.h:39, main.cu:72).  Device staging buffers are allocated on
+ * the first call and kept by the plan. */
+int tfft_exec_host(tfft_plan plan, const void* in_host, void* out_host, void* stream);
+
+/* Bytes of device memory the plan owns (tables + scratch + status). */
+size_t tfft_workspace_bytes(tfft_plan plan);
+
+/* Number of launches and, per launch i < 3: log2 of the sub-transform, lines
+ * per tile, points per thread, grid size, threads per block, dynamic shared
+ * memory bytes -- the quantities test_turbofft() derives at main.cu:22-32.
+ * info must hold 1 + 3*6 ints. */
+int tfft_plan_info(tfft_plan plan, int* info);
+
+/* The three literals fft_codegen.py bakes into the generated source
+ * (--err_inj, --err_smoothing, --err_threshold; fft_codegen.py:414,495,714-719)
+ * as run-time values.  Defaults: 100, 1000, 1e-3. */
+int tfft_set_ft_params(tfft_plan plan, double err_inj, double err_smoothing, double err_threshold);
+
+/* Fault site selection.  The reference injects into every block of the last
+ * launch (fft_codegen.py:412-415): that is launch = -1, period = 1, phase = 0
+ * and is the default when the plan was created with if_err.  period > 1 hits
+ * only blocks b with b % period == phase (sparse faults); launch selects which
+ * launch of a multi-launch plan is hit; enable = 0 turns injection off while
+ * keeping correction on. */
+int tfft_set_injection(tfft_plan plan, int enable, int launch, int period, int phase);
+
+/* FT outcome of the most recent tfft_exec (synchronises the plan's last
+ * stream).  n_detected / n_corrected: blocks whose checksum test fired / tiles
+ * recomputed, summed over launches.  located (may be NULL): for launch
+ * `launch`, the per-block located tile iteration, 1-based, -1 = nothing
+ * detected -- the register `k` of the reference kernels
+ * (fft_codegen.py:47,495), which the reference never exports.  At most cap
+ * entries are written; *n_blocks receives the launch's grid size. */
+int tfft_ft_status(tfft_plan plan, int* n_detected, int* n_corrected, int launch, int* located, int cap,
+                   int* n_blocks);
+
+/* Per-block checksum residuals of launch `launch` from the most recent exec:
+ * delta, S, delta_w as doubles, 3 per block (fft_codegen.py:432-495 keeps them
+ * in registers).  Only recorded after tfft_enable_ft_diag(plan, 1). */
+int tfft_enable_ft_diag(tfft_plan plan, int enable);
+int tfft_ft_diag(tfft_plan plan, int launch, double* diag, int cap_blocks);
+
+int tfft_plan_destroy(tfft_plan plan);
+
+/* Last CUDA error code seen by any call on this plan (0 = none). */
+int tfft_last_cuda_error(tfft_plan plan);
+const char* tfft_status_string(int status);
+
+/* Number of kernels this library launched since it was loaded (all plans). */
+long long tfft_launch_count(void);
+
+/* STREAM-style device copy with 128-bit loads and stores, used as the measured
+ * HBM peak every roofline fraction is quoted against. bytes must be a multiple
+ * of 16.  Stream ordered. */
+int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream);
+
+/* Building blocks of the multi-GPU four-step transform (no counterpart in the
+ * reference, which is single-GPU).  Both work on a local [rows][cols] complex
+ * matrix in device memory.
+ * tfft_transpose:         dst[c][r] = src[r][c]
+ * tfft_twiddle_transpose: dst[c][r] = src[r][c] * exp(-2*pi*i * (row0 + r) * (col0 + c) / 2^log_total)
+ */
+int tfft_transpose(const void* src, void* dst, long long rows, long long cols, int dtype, void* stream);
+int tfft_twiddle_transpose(const void* src, void* dst, long long rows, long long cols, long long row0,
+                           long long col0, int log_total, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOFFT_B200_H */

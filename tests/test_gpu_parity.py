@@ -1,0 +1,148 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle.
+
+Tolerances (relative L2 over the whole batch, float64 oracle):
+  complex64 : 1e-6  * log2 N
+  complex128: 1e-14 * log2 N
+"""
+import numpy as np
+import pytest
+
+from oracle import fft_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+CD = {0: np.complex64, 1: np.complex128}
+
+
+def run_plan(torch, logn, batch, dtype, x_np, **kw):
+    import turbofft_b200 as tf
+
+    plan = tf.Plan(logn, batch, dtype, **kw)
+    x = torch.from_numpy(x_np).cuda()
+    y = plan(x)
+    torch.cuda.synchronize()
+    out = y.cpu().numpy()
+    # the input must be untouched
+    assert torch.equal(x.cpu(), torch.from_numpy(x_np))
+    return plan, out
+
+
+def batch_for(logn, cap_log=18):
+    return max(3, min(1 << max(0, cap_log - logn), 300))
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn", list(range(1, 23)))
+def test_fft_matches_oracle(torch_cuda, logn, dtype):
+    batch = batch_for(logn) if logn < 17 else (3 if logn < 21 else 2)
+    x = orc.make_input(batch, 1 << logn, CD[dtype], seed=logn)
+    _, y = run_plan(torch_cuda, logn, batch, dtype, x)
+    err = orc.rel_l2(y, orc.fft_forward(x))
+    assert err <= orc.tolerance(CD[dtype], logn), (logn, dtype, err)
+    ok, idx, comp = orc.compare_data(y, orc.fft_forward(x).astype(CD[dtype]), 1e-4 * max(1, 1 << max(0, logn - 10)) if dtype == 0 else 1e-4)
+    assert ok or dtype == 0, (idx, comp)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn", [23, 24, 25])
+def test_three_launch_sizes(torch_cuda, logn, dtype):
+    x = orc.make_input(1, 1 << logn, CD[dtype], seed=logn)
+    _, y = run_plan(torch_cuda, logn, 1, dtype, x)
+    err = orc.rel_l2(y, orc.fft_forward(x))
+    assert err <= orc.tolerance(CD[dtype], logn), (logn, dtype, err)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn,batch", [(1, 1), (3, 1), (4, 129), (6, 17), (7, 1), (8, 33), (10, 5), (12, 1)])
+def test_ragged_batches(torch_cuda, logn, batch, dtype):
+    x = orc.make_input(batch, 1 << logn, CD[dtype], seed=100 + logn)
+    _, y = run_plan(torch_cuda, logn, batch, dtype, x)
+    assert orc.rel_l2(y, orc.fft_forward(x)) <= orc.tolerance(CD[dtype], logn)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn,batch,thread_bs", [(10, 64, 2), (10, 50, 4), (12, 7, 32), (16, 4, 8), (20, 2, 16), (5, 1000, 3)])
+def test_thread_bs(torch_cuda, logn, batch, thread_bs, dtype):
+    """Several tiles per block (the reference's --thread_bs), including tile counts that
+    do not divide (the reference drops the remainder, main.cu:32; here it is computed)."""
+    x = orc.make_input(batch, 1 << logn, CD[dtype], seed=7)
+    _, y = run_plan(torch_cuda, logn, batch, dtype, x, thread_bs=thread_bs)
+    assert orc.rel_l2(y, orc.fft_forward(x)) <= orc.tolerance(CD[dtype], logn)
+
+
+def test_config1_readme_case(torch_cuda):
+    """N = 2^10, batch 16, complex64, uniform[-1,1) seed 0 (the README's verify case)."""
+    x = orc.make_input(16, 1024, np.complex64, seed=0)
+    _, y = run_plan(torch_cuda, 10, 16, 0, x)
+    ref = orc.fft_forward(x)
+    assert orc.rel_l2(y, ref) <= orc.tolerance(np.complex64, 10)
+    ok, idx, comp = orc.compare_data(y, ref.astype(np.complex64), 1e-4)
+    assert ok, (idx, comp)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_analytic_identities(torch_cuda, dtype):
+    n = 4096
+    imp = np.zeros((2, n), CD[dtype])
+    imp[0, 0] = 1
+    imp[1, 5] = 1
+    _, y = run_plan(torch_cuda, 12, 2, dtype, imp)
+    assert np.allclose(y[0], 1, atol=1e-6)
+    k = np.arange(n)
+    assert np.allclose(y[1], np.exp(-2j * np.pi * 5 * k / n), atol=1e-5 if dtype == 0 else 1e-12)
+    ones = np.ones((1, n), CD[dtype])
+    _, y = run_plan(torch_cuda, 12, 1, dtype, ones)
+    expect = np.zeros(n, complex)
+    expect[0] = n
+    assert np.allclose(y[0], expect, atol=1e-2 if dtype == 0 else 1e-9)
+
+
+@pytest.mark.parametrize("logn", [9, 15])
+def test_in_place(torch_cuda, logn):
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    xn = orc.make_input(4, 1 << logn, np.complex64, seed=3)
+    x = torch.from_numpy(xn).cuda()
+    plan = tf.Plan(logn, 4, 0)
+    plan(x, out=x)
+    torch.cuda.synchronize()
+    assert orc.rel_l2(x.cpu().numpy(), orc.fft_forward(xn)) <= orc.tolerance(np.complex64, logn)
+
+
+def test_torch_entry_point(torch_cuda):
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    x = torch.randn(3, 5, 256, dtype=torch.complex128, device="cuda")
+    y = tf.fft(x)
+    ref = torch.fft.fft(x.cpu())
+    assert (y.cpu() - ref).abs().max() < 1e-10
+    x32 = torch.randn(8, 2048, dtype=torch.complex64, device="cuda")
+    y32 = tf.fft(x32)
+    ref32 = np.fft.fft(x32.cpu().numpy().astype(np.complex128))
+    assert orc.rel_l2(y32.cpu().numpy(), ref32) <= 1.1e-5
+
+
+def test_exec_host(torch_cuda):
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    xn = orc.make_input(32, 2048, np.complex64, seed=11)
+    x = torch.from_numpy(xn).pin_memory()
+    plan = tf.Plan(11, 32, 0)
+    y = plan.exec_host(x)
+    assert orc.rel_l2(y.numpy(), orc.fft_forward(xn)) <= orc.tolerance(np.complex64, 11)
+
+
+def test_errors(torch_cuda):
+    import turbofft_b200 as tf
+
+    with pytest.raises(tf.TurboFFTError):
+        tf.Plan(0, 1, 0)
+    with pytest.raises(tf.TurboFFTError):
+        tf.Plan(31, 1, 0)
+    with pytest.raises(tf.TurboFFTError):
+        tf.Plan(10, 0, 0)
+    with pytest.raises(tf.TurboFFTError):
+        tf.Plan(10, 4, 0, param_csv="/nonexistent/param.csv")

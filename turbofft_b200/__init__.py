@@ -1,0 +1,169 @@
+"""turbofft_b200: batched power-of-two C2C FFT with fused ABFT for B200 (sm_100a).
+
+Python face of the C ABI (include/turbofft_b200.h).  `Plan` mirrors the launch
+protocol of the reference's test_turbofft() (main.cu:4-73) with the CLI's flag names
+(--logN, --bs as `batch`, --datatype, --if_ft, --if_err, --thread_bs;
+include/utils/CommandLineParser.h:47-79); `fft` is the torch-style entry point for
+complex64 / complex128 CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+from . import _lib
+from ._lib import TurboFFTError, lib
+
+__all__ = ["Plan", "fft", "TurboFFTError", "lib", "stream_copy", "launch_count"]
+
+FLOAT2, DOUBLE2 = 0, 1
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _dtype_code(t) -> int:
+    torch = _torch()
+    if t == torch.complex64:
+        return FLOAT2
+    if t == torch.complex128:
+        return DOUBLE2
+    raise TypeError(f"turbofft_b200 supports complex64 and complex128, got {t}")
+
+
+class Plan:
+    """One (logN, batch, dtype, FT mode) plan on one device."""
+
+    def __init__(self, logN: int, batch: int, dtype: int = FLOAT2, if_ft: int = 0, if_err: int = 0,
+                 thread_bs: int = 1, param_csv: Optional[str] = None, device: int = 0):
+        self._h = C.c_void_p()
+        self.logN, self.batch, self.dtype = int(logN), int(batch), int(dtype)
+        self.if_ft, self.if_err, self.thread_bs, self.device = int(bool(if_ft or if_err)), int(if_err), int(thread_bs), int(device)
+        rc = lib().tfft_plan_create(C.byref(self._h), self.logN, self.batch, self.dtype, int(if_ft), int(if_err),
+                                    self.thread_bs, param_csv.encode() if param_csv else None, self.device)
+        _lib.check(rc, f"tfft_plan_create(logN={logN}, batch={batch}, dtype={dtype}, ft={if_ft}, err={if_err})")
+
+    # -- execution
+    def exec_ptr(self, in_ptr: int, out_ptr: int, stream: int = 0) -> None:
+        _lib.check(lib().tfft_exec(self._h, in_ptr, out_ptr, stream), "tfft_exec", self._h)
+
+    def exec_host_ptr(self, in_ptr: int, out_ptr: int, stream: int = 0) -> None:
+        _lib.check(lib().tfft_exec_host(self._h, in_ptr, out_ptr, stream), "tfft_exec_host", self._h)
+
+    def __call__(self, x, out=None):
+        """x: CUDA tensor [batch, N] (or [N] when batch == 1) of the plan's dtype."""
+        torch = _torch()
+        if not x.is_cuda:
+            raise ValueError("input must be a CUDA tensor (use exec_host for host buffers)")
+        if _dtype_code(x.dtype) != self.dtype or x.numel() != self.batch << self.logN:
+            raise ValueError("tensor does not match the plan")
+        if x.device.index != self.device:
+            raise ValueError("tensor is on another device than the plan")
+        x = x.contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        elif not (out.is_cuda and out.is_contiguous() and out.dtype == x.dtype and out.numel() == x.numel()):
+            raise ValueError("bad output tensor")
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        self.exec_ptr(x.data_ptr(), out.data_ptr(), stream)
+        return out
+
+    def exec_host(self, x, out=None):
+        """x: CPU tensor (pinned for full speed); returns a CPU tensor.  Synchronous."""
+        torch = _torch()
+        if x.is_cuda or _dtype_code(x.dtype) != self.dtype or x.numel() != self.batch << self.logN:
+            raise ValueError("tensor does not match the plan")
+        x = x.contiguous()
+        if out is None:
+            out = torch.empty_like(x, pin_memory=x.is_pinned())
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self.exec_host_ptr(x.data_ptr(), out.data_ptr(), stream)
+        return out
+
+    # -- introspection
+    def info(self):
+        buf = (C.c_int * 19)()
+        _lib.check(lib().tfft_plan_info(self._h, buf), "tfft_plan_info", self._h)
+        keys = ("logNi", "lines_per_tile", "points_per_thread", "grid", "threads", "smem_bytes")
+        return [dict(zip(keys, buf[1 + 6 * i: 7 + 6 * i])) for i in range(buf[0])]
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(lib().tfft_workspace_bytes(self._h))
+
+    # -- fault tolerance
+    def set_ft_params(self, err_inj: float = 100.0, err_smoothing: float = 1000.0, err_threshold: float = 1e-3):
+        _lib.check(lib().tfft_set_ft_params(self._h, err_inj, err_smoothing, err_threshold), "tfft_set_ft_params")
+
+    def set_injection(self, enable: bool = True, launch: int = -1, period: int = 1, phase: int = 0):
+        _lib.check(lib().tfft_set_injection(self._h, int(enable), launch, period, phase), "tfft_set_injection")
+
+    def enable_ft_diag(self, enable: bool = True):
+        _lib.check(lib().tfft_enable_ft_diag(self._h, int(enable)), "tfft_enable_ft_diag")
+
+    def ft_status(self, launch: int = -1):
+        """(n_detected, n_corrected, located[list per block of `launch`])."""
+        nd, nc, nb = C.c_int(), C.c_int(), C.c_int()
+        _lib.check(lib().tfft_ft_status(self._h, C.byref(nd), C.byref(nc), launch, None, 0, C.byref(nb)),
+                   "tfft_ft_status", self._h)
+        loc = (C.c_int * max(nb.value, 1))()
+        _lib.check(lib().tfft_ft_status(self._h, C.byref(nd), C.byref(nc), launch, loc, nb.value, C.byref(nb)),
+                   "tfft_ft_status", self._h)
+        return nd.value, nc.value, list(loc[: nb.value])
+
+    def ft_diag(self, launch: int = -1):
+        """Per block (delta, S, delta_w) of `launch`; needs enable_ft_diag() before exec."""
+        _, _, loc = self.ft_status(launch)
+        buf = (C.c_double * (3 * max(len(loc), 1)))()
+        _lib.check(lib().tfft_ft_diag(self._h, launch, buf, len(loc)), "tfft_ft_diag", self._h)
+        return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(len(loc))]
+
+    def destroy(self):
+        if self._h:
+            lib().tfft_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+_plan_cache = {}
+
+
+def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None):
+    """Forward unnormalised FFT along the last axis of a complex64/complex128 CUDA tensor.
+
+    Power-of-two lengths 2..2^30; leading axes are the batch.  ft/err are the
+    reference's --if_ft / --if_err.  Plans are cached per (device, shape, mode).
+    """
+    n = x.shape[-1]
+    logn = n.bit_length() - 1
+    if n < 2 or (1 << logn) != n:
+        raise ValueError("last axis must be a power of two >= 2")
+    batch = x.numel() // n
+    key = (x.device.index, logn, batch, _dtype_code(x.dtype), bool(ft), bool(err), thread_bs)
+    plan = _plan_cache.get(key)
+    if plan is None:
+        plan = Plan(logn, batch, _dtype_code(x.dtype), int(ft or err), int(err), thread_bs, device=x.device.index)
+        _plan_cache[key] = plan
+    y = plan(x.reshape(batch, n), out=None if out is None else out.reshape(batch, n))
+    return y.reshape(x.shape)
+
+
+def stream_copy(src, dst) -> None:
+    """STREAM-style device copy (128-bit accesses) used as the measured HBM peak."""
+    torch = _torch()
+    nbytes = src.numel() * src.element_size()
+    stream = torch.cuda.current_stream(src.device).cuda_stream
+    _lib.check(lib().tfft_stream_copy(src.data_ptr(), dst.data_ptr(), nbytes, stream), "tfft_stream_copy")
+
+
+def launch_count() -> int:
+    return int(lib().tfft_launch_count())

@@ -1,0 +1,77 @@
+"""ctypes binding of libturbofft_b200.so (the C ABI of include/turbofft_b200.h).
+
+The library is the only compute path: if it is missing this module raises, it never
+falls back to another FFT.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libturbofft_b200.so")
+
+TFFT_OK = 0
+STATUS = {
+    0: "TFFT_OK", -1: "TFFT_ERR_BAD_ARG", -2: "TFFT_ERR_UNSUPPORTED", -3: "TFFT_ERR_CUDA",
+    -4: "TFFT_ERR_PARAM_FILE", -5: "TFFT_ERR_ALLOC", -6: "TFFT_ERR_TOO_LARGE",
+}
+
+# name -> (restype, argtypes); every symbol include/turbofft_b200.h declares
+SIGNATURES = {
+    "tfft_plan_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.c_char_p, C.c_int]),
+    "tfft_exec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tfft_exec_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tfft_workspace_bytes": (C.c_size_t, [C.c_void_p]),
+    "tfft_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "tfft_set_ft_params": (C.c_int, [C.c_void_p, C.c_double, C.c_double, C.c_double]),
+    "tfft_set_injection": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tfft_ft_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int),
+                                 C.c_int, C.POINTER(C.c_int)]),
+    "tfft_enable_ft_diag": (C.c_int, [C.c_void_p, C.c_int]),
+    "tfft_ft_diag": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.c_int]),
+    "tfft_plan_destroy": (C.c_int, [C.c_void_p]),
+    "tfft_last_cuda_error": (C.c_int, [C.c_void_p]),
+    "tfft_status_string": (C.c_char_p, [C.c_int]),
+    "tfft_launch_count": (C.c_longlong, []),
+    "tfft_stream_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "tfft_transpose": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p]),
+    "tfft_twiddle_transpose": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
+                                         C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+}
+
+_lib = None
+
+
+class TurboFFTError(RuntimeError):
+    def __init__(self, status: int, where: str, cuda_error: int = 0):
+        self.status = status
+        self.cuda_error = cuda_error
+        msg = f"{where}: {STATUS.get(status, status)}"
+        if cuda_error:
+            msg += f" (CUDA error {cuda_error})"
+        super().__init__(msg)
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m turbofft_b200.build` "
+                "(there is no fallback path)")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(status: int, where: str, plan=None) -> None:
+    if status != TFFT_OK:
+        cuda = lib().tfft_last_cuda_error(plan) if plan else 0
+        raise TurboFFTError(status, where, cuda)

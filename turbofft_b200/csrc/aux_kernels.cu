@@ -1,0 +1,113 @@
+// Helper kernels behind the C ABI that are not FFT launches: the STREAM-style copy
+// that measures the HBM peak every roofline fraction is quoted against, and the
+// (twiddled) transposes the multi-GPU four-step transform is assembled from.
+#include <cuda_runtime.h>
+
+#include "../../include/turbofft_b200.h"
+#include "registry.h"
+
+namespace {
+
+__global__ void __launch_bounds__(256) stream_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                          size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // four independent 128-bit loads in flight per thread
+    for (; i + 3 * stride < n; i += 4 * stride) {
+        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+        dst[i] = a;
+        dst[i + stride] = b;
+        dst[i + 2 * stride] = c;
+        dst[i + 3 * stride] = d;
+    }
+    for (; i < n; i += stride) dst[i] = src[i];
+}
+
+template <typename C> struct RealOf;
+template <> struct RealOf<float2> { typedef float type; };
+template <> struct RealOf<double2> { typedef double type; };
+
+// 32x32 tile transpose through padded shared memory; TW multiplies by
+// exp(-2*pi*i*(row0+r)*(col0+c)/2^log_total), evaluated with sincospi in double so
+// that the integer phase (r*c mod 2^log_total) is reduced exactly.
+template <typename C, bool TW>
+__global__ void __launch_bounds__(256) transpose_kernel(const C* __restrict__ src, C* __restrict__ dst, long long rows,
+                                                        long long cols, long long row0, long long col0, int log_total) {
+    __shared__ C tile[32][33];
+    const long long tiles_c = (cols + 31) / 32;
+    const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long r = tr * 32 + ty + 8 * k, c = tc * 32 + tx;
+        if (r < rows && c < cols) {
+            C v = src[r * cols + c];
+            if (TW) {
+                typedef typename RealOf<C>::type T;
+                const unsigned long long mask = (1ULL << log_total) - 1;
+                const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)(col0 + c)) & mask;
+                double sn, cs;
+                sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
+                C w;
+                w.x = (T)(v.x * cs - v.y * sn);
+                w.y = (T)(v.x * sn + v.y * cs);
+                v = w;
+            }
+            tile[ty + 8 * k][tx] = v;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long c = tc * 32 + ty + 8 * k, r = tr * 32 + tx;
+        if (r < rows && c < cols) dst[c * rows + r] = tile[tx][ty + 8 * k];
+    }
+}
+
+template <bool TW>
+int launch_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
+                     int log_total, int dtype, void* stream) {
+    if (!src || !dst || rows < 1 || cols < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2)) return TFFT_ERR_BAD_ARG;
+    if (TW && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
+    const long long blocks = ((rows + 31) / 32) * ((cols + 31) / 32);
+    if (blocks > 2147483647LL) return TFFT_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == TFFT_FLOAT2)
+        transpose_kernel<float2, TW><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, (float2*)dst, rows, cols, row0,
+                                                                      col0, log_total);
+    else
+        transpose_kernel<double2, TW><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, (double2*)dst, rows, cols,
+                                                                        row0, col0, log_total);
+    tfft::note_launch();
+    return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream) {
+    if (!src || !dst || (bytes & 15) || (((size_t)src | (size_t)dst) & 15)) return TFFT_ERR_BAD_ARG;
+    const size_t n = bytes / 16;
+    if (n == 0) return TFFT_OK;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TFFT_ERR_CUDA;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t blocks = (n + 255) / 256;
+    const size_t cap = (size_t)sms * 8;  // 2048 threads per SM
+    if (blocks > cap) blocks = cap;
+    stream_copy_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, n);
+    tfft::note_launch();
+    return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+int tfft_transpose(const void* src, void* dst, long long rows, long long cols, int dtype, void* stream) {
+    return launch_transpose<false>(src, dst, rows, cols, 0, 0, 1, dtype, stream);
+}
+
+int tfft_twiddle_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
+                           int log_total, int dtype, void* stream) {
+    return launch_transpose<true>(src, dst, rows, cols, row0, col0, log_total, dtype, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,494 @@
+// Host side of the C ABI declared in include/turbofft_b200.h: launch planner, table
+// builders and the exec loop.  It stands where test_turbofft() / TurboFFT_main()
+// stand in the reference (main.cu:4-73, 75-135) but owns its tables, checks every
+// CUDA call and never synchronises inside exec.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/turbofft_b200.h"
+#include "fft_kernels.cuh"
+#include "generated/ft_defaults.h"
+#include "params.h"
+#include "registry.h"
+
+using namespace tfft;
+
+namespace {
+
+std::atomic<long long> g_launches{0};
+
+struct LaunchDesc {
+    int role = 0, logm = 0, loge = 0, logc = 0;
+    const KernelEntry* k = nullptr;
+    long long n_tiles = 0;
+    long long n_lines = 0;
+    unsigned grid = 0;
+    int log_b = 0, log_n1 = 0, log_q = 0, tw_lo_bits = 0;
+    void* tw_m = nullptr;
+    void* tw_lo = nullptr;
+    void* tw_hi = nullptr;
+    void* cks = nullptr;
+    int* ft_located = nullptr;
+    void* ft_diag = nullptr;
+};
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+        if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+}  // namespace
+
+struct tfft_plan_s {
+    int logn = 0;
+    long long batch = 0;
+    int dtype = 0, if_ft = 0, if_err = 0, thread_bs = 1, device = 0;
+    int n_launch = 0;
+    LaunchDesc L[3];
+    void* scratch = nullptr;
+    unsigned int* ft_count = nullptr;  // [3][2]
+    size_t owned_bytes = 0;
+    double err_inj = TFFT_DEFAULT_ERR_INJ;
+    double err_smoothing = TFFT_DEFAULT_ERR_SMOOTHING;
+    double err_threshold = TFFT_DEFAULT_ERR_THRESHOLD;
+    int inj_enable = 0, inj_launch = -1, inj_period = 1, inj_phase = 0;
+    int diag = 0;
+    cudaStream_t last_stream = nullptr;
+    int last_cuda_error = 0;
+    void* stage_in = nullptr;
+    void* stage_out = nullptr;
+    std::vector<void*> allocs;
+    size_t esize() const { return dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2); }
+};
+
+namespace {
+
+bool cuda_ok(tfft_plan p, cudaError_t e) {
+    if (e == cudaSuccess) return true;
+    if (p) p->last_cuda_error = (int)e;
+    return false;
+}
+
+void* dev_alloc(tfft_plan p, size_t bytes) {
+    void* ptr = nullptr;
+    if (!cuda_ok(p, cudaMalloc(&ptr, bytes ? bytes : 16))) return nullptr;
+    p->allocs.push_back(ptr);
+    p->owned_bytes += bytes;
+    return ptr;
+}
+
+// exp(-2*pi*i*j/2^logp) in extended precision, then rounded once to T.
+template <typename C>
+void fill_twiddles(std::vector<C>& v, long long count, long long stride, int logp) {
+    v.resize((size_t)count);
+    const long double two_pi = 6.283185307179586476925286766559005768L;
+    const long double pn = std::ldexp(1.0L, logp);
+    for (long long j = 0; j < count; ++j) {
+        const long long idx = (j * stride) & (((long long)1 << logp) - 1);
+        const long double ang = -two_pi * (long double)idx / pn;
+        v[(size_t)j].x = (decltype(v[0].x))cosl(ang);
+        v[(size_t)j].y = (decltype(v[0].y))sinl(ang);
+    }
+}
+
+// c = W_M r with r_j = omega^(j mod 3): the ABFT encoding vector of
+// getDFTMatrixChecksum() (include/utils/abft.h:21-61), evaluated as the FFT of r in
+// extended precision instead of the reference's O(M^2) float-angle loop.
+void checksum_vector(int logm, std::vector<long double>& re, std::vector<long double>& im) {
+    const int m = 1 << logm;
+    re.assign(m, 0);
+    im.assign(m, 0);
+    const long double h = 0.8660253882408142L;  // float32-rounded sqrt(3)/2, as in constants.h:2-7
+    const long double rr[3] = {1.0L, -0.5L, -0.5L};
+    const long double ri[3] = {0.0L, -h, h};
+    // bit-reversed load, then iterative radix-2 DIT
+    for (int j = 0; j < m; ++j) {
+        int r = 0;
+        for (int b = 0; b < logm; ++b) r |= ((j >> b) & 1) << (logm - 1 - b);
+        re[r] = rr[j % 3];
+        im[r] = ri[j % 3];
+    }
+    const long double two_pi = 6.283185307179586476925286766559005768L;
+    for (int len = 2; len <= m; len <<= 1) {
+        for (int k = 0; k < len / 2; ++k) {
+            const long double ang = -two_pi * (long double)k / (long double)len;
+            const long double wr = cosl(ang), wi = sinl(ang);
+            for (int s = 0; s < m; s += len) {
+                const int a = s + k, b = s + k + len / 2;
+                const long double tr = re[b] * wr - im[b] * wi;
+                const long double ti = re[b] * wi + im[b] * wr;
+                re[b] = re[a] - tr;
+                im[b] = im[a] - ti;
+                re[a] += tr;
+                im[a] += ti;
+            }
+        }
+    }
+}
+
+template <typename C>
+bool upload(tfft_plan p, const std::vector<C>& host, void** dev) {
+    *dev = dev_alloc(p, host.size() * sizeof(C));
+    if (!*dev) return false;
+    return cuda_ok(p, cudaMemcpy(*dev, host.data(), host.size() * sizeof(C), cudaMemcpyHostToDevice));
+}
+
+template <typename T>
+bool build_tables(tfft_plan p) {
+    typedef typename Cplx<T>::type C;
+    for (int i = 0; i < p->n_launch; ++i) {
+        LaunchDesc& d = p->L[i];
+        // reuse tables of an earlier launch with the same line length
+        int same = -1;
+        for (int j = 0; j < i; ++j)
+            if (p->L[j].logm == d.logm) same = j;
+        if (same >= 0) {
+            d.tw_m = p->L[same].tw_m;
+            d.cks = p->L[same].cks;
+        } else {
+            std::vector<C> t;
+            fill_twiddles(t, 1LL << d.logm, 1, d.logm);
+            if (!upload(p, t, &d.tw_m)) return false;
+            if (p->if_ft) {
+                std::vector<long double> re, im;
+                checksum_vector(d.logm, re, im);
+                std::vector<C> c(re.size());
+                for (size_t k = 0; k < re.size(); ++k) {
+                    c[k].x = (T)re[k];
+                    c[k].y = (T)im[k];
+                }
+                if (!upload(p, c, &d.cks)) return false;
+            }
+        }
+        if (d.role == ROLE_FIRST) {
+            const int logp = d.logm + d.log_b;
+            d.tw_lo_bits = (logp + 1) / 2;
+            std::vector<C> lo, hi;
+            fill_twiddles(lo, 1LL << d.tw_lo_bits, 1, logp);
+            fill_twiddles(hi, 1LL << (logp - d.tw_lo_bits), 1LL << d.tw_lo_bits, logp);
+            if (!upload(p, lo, &d.tw_lo) || !upload(p, hi, &d.tw_hi)) return false;
+        }
+    }
+    return true;
+}
+
+int ilog2_exact(long long x) {
+    int l = 0;
+    while ((1LL << l) < x) ++l;
+    return ((1LL << l) == x) ? l : -1;
+}
+
+template <typename T>
+int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
+    typedef typename Cplx<T>::type C;
+    const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
+    if (p->if_ft) {
+        if (!cuda_ok(p, cudaMemsetAsync(p->ft_count, 0, 6 * sizeof(unsigned int), st))) return TFFT_ERR_CUDA;
+    }
+    const int inj_launch = p->inj_launch < 0 ? p->n_launch - 1 : p->inj_launch;
+    for (int i = 0; i < p->n_launch; ++i) {
+        const LaunchDesc& d = p->L[i];
+        KernelArgs<T> a;
+        memset(&a, 0, sizeof(a));
+        a.in = (const C*)(i == 0 ? in : p->scratch);
+        a.out = (C*)(i == p->n_launch - 1 ? out : p->scratch);
+        a.tw_m = (const C*)d.tw_m;
+        a.tw_lo = (const C*)d.tw_lo;
+        a.tw_hi = (const C*)d.tw_hi;
+        a.cks = (const C*)d.cks;
+        a.n_tiles = d.n_tiles;
+        a.n_lines = d.n_lines;
+        a.tiles_per_cta = p->thread_bs;
+        a.log_n = p->logn;
+        a.log_b = d.log_b;
+        a.log_n1 = d.log_n1;
+        a.log_q = d.log_q;
+        a.tw_lo_bits = d.tw_lo_bits;
+        a.inj_on = (p->if_err && p->inj_enable && i == inj_launch) ? 1 : 0;
+        a.inj_period = p->inj_period;
+        a.inj_phase = p->inj_phase;
+        a.err_inj = (T)p->err_inj;
+        a.err_smoothing = (T)p->err_smoothing;
+        a.err_threshold = (T)p->err_threshold;
+        a.ft_located = d.ft_located;
+        a.ft_count = p->ft_count ? p->ft_count + 2 * i : nullptr;
+        a.ft_diag = p->diag ? (T*)d.ft_diag : nullptr;
+        void* args[] = {&a};
+        const void* fn = d.k->fn[ftmode];
+        if (!cuda_ok(p, cudaLaunchKernel(fn, dim3(d.grid), dim3(d.k->threads), args, d.k->smem, st)))
+            return TFFT_ERR_CUDA;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return TFFT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int if_ft, int if_err, int thread_bs,
+                     const char* param_csv, int device) {
+    if (!plan) return TFFT_ERR_BAD_ARG;
+    *plan = nullptr;
+    if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 1 ||
+        device < 0)
+        return TFFT_ERR_BAD_ARG;
+    if (if_err) if_ft = 1;  // as the reference CLI does (CommandLineParser.h:62-64)
+    std::vector<ParamRow> rows;
+    std::string err;
+    if (param_csv && param_csv[0]) {
+        if (!load_param_file(param_csv, rows, err)) return TFFT_ERR_PARAM_FILE;
+    } else {
+        if (!parse_param_csv(builtin_param_csv(dtype), rows, err)) return TFFT_ERR_PARAM_FILE;
+    }
+    if ((int)rows.size() <= logN || rows[logN].launches == 0) return TFFT_ERR_UNSUPPORTED;
+    const ParamRow& row = rows[logN];
+    if (!validate_row(row, err)) return TFFT_ERR_PARAM_FILE;
+
+    DeviceGuard guard(device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+
+    tfft_plan p = new (std::nothrow) tfft_plan_s();
+    if (!p) return TFFT_ERR_ALLOC;
+    p->logn = logN;
+    p->batch = batch;
+    p->dtype = dtype;
+    p->if_ft = if_ft ? 1 : 0;
+    p->if_err = if_err ? 1 : 0;
+    p->inj_enable = p->if_err;
+    p->thread_bs = thread_bs;
+    p->device = device;
+    p->n_launch = row.launches;
+    const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
+
+    int status = TFFT_OK;
+    long long outer = batch;  // product of batch and the digits already transformed
+    int log_rest = logN;      // log2 of the not yet transformed extent, including this launch
+    for (int i = 0; i < row.launches && status == TFFT_OK; ++i) {
+        LaunchDesc& d = p->L[i];
+        d.logm = row.logni[i];
+        d.logc = ilog2_exact(row.bs[i]);
+        d.loge = ilog2_exact(row.n[i]);
+        if (d.loge > d.logm) d.loge = d.logm;
+        d.role = row.launches == 1 ? ROLE_SINGLE : (i == row.launches - 1 ? ROLE_LAST : ROLE_FIRST);
+        log_rest -= d.logm;
+        if (d.role == ROLE_SINGLE) {
+            d.n_lines = batch;
+            d.n_tiles = (batch + (1LL << d.logc) - 1) >> d.logc;
+        } else if (d.role == ROLE_FIRST) {
+            d.log_b = log_rest;
+            if (d.log_b < d.logc) d.logc = d.log_b;  // fewer columns than a tile is wide
+            d.n_tiles = outer << (d.log_b - d.logc);
+        } else {
+            d.log_n1 = row.logni[0];
+            d.log_q = row.launches == 3 ? row.logni[1] : 0;
+            if (d.log_n1 < d.logc) d.logc = d.log_n1;
+            d.n_tiles = (batch << (logN - d.logm)) >> d.logc;
+        }
+        outer <<= d.logm;
+        d.k = find_kernel(dtype, d.role, d.logm, d.loge, d.logc);
+        if (!d.k || !d.k->fn[ftmode]) {
+            status = TFFT_ERR_UNSUPPORTED;
+            break;
+        }
+        const long long grid = (d.n_tiles + thread_bs - 1) / thread_bs;
+        if (grid > 2147483647LL) {
+            status = TFFT_ERR_TOO_LARGE;
+            break;
+        }
+        d.grid = (unsigned)grid;
+        if (d.k->smem > 48 * 1024) {
+            if (!cuda_ok(p, cudaFuncSetAttribute(d.k->fn[ftmode], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)d.k->smem)))
+                status = TFFT_ERR_CUDA;
+        }
+    }
+    if (status == TFFT_OK) {
+        const bool ok = dtype == TFFT_FLOAT2 ? build_tables<float>(p) : build_tables<double>(p);
+        if (!ok) status = p->last_cuda_error ? TFFT_ERR_CUDA : TFFT_ERR_ALLOC;
+    }
+    if (status == TFFT_OK && p->n_launch > 1) {
+        p->scratch = dev_alloc(p, ((size_t)batch << logN) * p->esize());
+        if (!p->scratch) status = TFFT_ERR_ALLOC;
+    }
+    if (status == TFFT_OK && p->if_ft) {
+        p->ft_count = (unsigned int*)dev_alloc(p, 6 * sizeof(unsigned int));
+        if (!p->ft_count) status = TFFT_ERR_ALLOC;
+        for (int i = 0; i < p->n_launch && status == TFFT_OK; ++i) {
+            p->L[i].ft_located = (int*)dev_alloc(p, (size_t)p->L[i].grid * sizeof(int));
+            p->L[i].ft_diag = dev_alloc(p, (size_t)p->L[i].grid * 3 * (p->esize() / 2));
+            if (!p->L[i].ft_located || !p->L[i].ft_diag) status = TFFT_ERR_ALLOC;
+        }
+    }
+    if (status != TFFT_OK) {
+        for (void* q : p->allocs) cudaFree(q);
+        delete p;
+        return status;
+    }
+    *plan = p;
+    return TFFT_OK;
+}
+
+int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
+    if (!p || !in || !out) return TFFT_ERR_BAD_ARG;
+    if (in == out && p->n_launch == 1 && p->if_err) return TFFT_ERR_UNSUPPORTED;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    p->last_stream = st;
+    return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st) : launch_all<double>(p, in, out, st);
+}
+
+int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* stream) {
+    if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    const size_t bytes = ((size_t)p->batch << p->logn) * p->esize();
+    if (!p->stage_in) {
+        p->stage_in = dev_alloc(p, bytes);
+        p->stage_out = dev_alloc(p, bytes);
+        if (!p->stage_in || !p->stage_out) return TFFT_ERR_ALLOC;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!cuda_ok(p, cudaMemcpyAsync(p->stage_in, in_host, bytes, cudaMemcpyHostToDevice, st))) return TFFT_ERR_CUDA;
+    const int rc = tfft_exec(p, p->stage_in, p->stage_out, stream);
+    if (rc != TFFT_OK) return rc;
+    if (!cuda_ok(p, cudaMemcpyAsync(out_host, p->stage_out, bytes, cudaMemcpyDeviceToHost, st))) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaStreamSynchronize(st))) return TFFT_ERR_CUDA;
+    return TFFT_OK;
+}
+
+size_t tfft_workspace_bytes(tfft_plan p) { return p ? p->owned_bytes : 0; }
+
+int tfft_plan_info(tfft_plan p, int* info) {
+    if (!p || !info) return TFFT_ERR_BAD_ARG;
+    info[0] = p->n_launch;
+    for (int i = 0; i < 3; ++i) {
+        int* o = info + 1 + 6 * i;
+        if (i < p->n_launch) {
+            const LaunchDesc& d = p->L[i];
+            o[0] = d.logm;
+            o[1] = 1 << d.logc;
+            o[2] = 1 << d.loge;
+            o[3] = (int)d.grid;
+            o[4] = d.k->threads;
+            o[5] = (int)d.k->smem;
+        } else {
+            for (int j = 0; j < 6; ++j) o[j] = 0;
+        }
+    }
+    return TFFT_OK;
+}
+
+int tfft_set_ft_params(tfft_plan p, double err_inj, double err_smoothing, double err_threshold) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    p->err_inj = err_inj;
+    p->err_smoothing = err_smoothing;
+    p->err_threshold = err_threshold;
+    return TFFT_OK;
+}
+
+int tfft_set_injection(tfft_plan p, int enable, int launch, int period, int phase) {
+    if (!p || period < 1 || phase < 0 || phase >= period || launch >= p->n_launch) return TFFT_ERR_BAD_ARG;
+    p->inj_enable = enable ? 1 : 0;
+    p->inj_launch = launch;
+    p->inj_period = period;
+    p->inj_phase = phase;
+    return TFFT_OK;
+}
+
+int tfft_ft_status(tfft_plan p, int* n_detected, int* n_corrected, int launch, int* located, int cap, int* n_blocks) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    if (n_detected) *n_detected = 0;
+    if (n_corrected) *n_corrected = 0;
+    if (n_blocks) *n_blocks = 0;
+    if (!p->if_ft) return TFFT_OK;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaStreamSynchronize(p->last_stream))) return TFFT_ERR_CUDA;
+    unsigned int cnt[6];
+    if (!cuda_ok(p, cudaMemcpy(cnt, p->ft_count, sizeof(cnt), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
+    for (int i = 0; i < p->n_launch; ++i) {
+        if (n_detected) *n_detected += (int)cnt[2 * i];
+        if (n_corrected) *n_corrected += (int)cnt[2 * i + 1];
+    }
+    if (launch < 0) launch = p->n_launch - 1;
+    if (launch >= p->n_launch) return TFFT_ERR_BAD_ARG;
+    if (n_blocks) *n_blocks = (int)p->L[launch].grid;
+    if (located && cap > 0) {
+        const size_t n = (size_t)(cap < (int)p->L[launch].grid ? cap : (int)p->L[launch].grid);
+        if (!cuda_ok(p, cudaMemcpy(located, p->L[launch].ft_located, n * sizeof(int), cudaMemcpyDeviceToHost)))
+            return TFFT_ERR_CUDA;
+    }
+    return TFFT_OK;
+}
+
+int tfft_enable_ft_diag(tfft_plan p, int enable) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    p->diag = enable ? 1 : 0;
+    return TFFT_OK;
+}
+
+int tfft_ft_diag(tfft_plan p, int launch, double* diag, int cap_blocks) {
+    if (!p || !diag || !p->if_ft) return TFFT_ERR_BAD_ARG;
+    if (launch < 0) launch = p->n_launch - 1;
+    if (launch >= p->n_launch) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaStreamSynchronize(p->last_stream))) return TFFT_ERR_CUDA;
+    const size_t n = 3 * (size_t)(cap_blocks < (int)p->L[launch].grid ? cap_blocks : (int)p->L[launch].grid);
+    if (p->dtype == TFFT_FLOAT2) {
+        std::vector<float> tmp(n);
+        if (!cuda_ok(p, cudaMemcpy(tmp.data(), p->L[launch].ft_diag, n * sizeof(float), cudaMemcpyDeviceToHost)))
+            return TFFT_ERR_CUDA;
+        for (size_t i = 0; i < n; ++i) diag[i] = tmp[i];
+    } else {
+        if (!cuda_ok(p, cudaMemcpy(diag, p->L[launch].ft_diag, n * sizeof(double), cudaMemcpyDeviceToHost)))
+            return TFFT_ERR_CUDA;
+    }
+    return TFFT_OK;
+}
+
+int tfft_plan_destroy(tfft_plan p) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(p->device);
+    for (void* q : p->allocs) cudaFree(q);
+    delete p;
+    return TFFT_OK;
+}
+
+int tfft_last_cuda_error(tfft_plan p) { return p ? p->last_cuda_error : 0; }
+
+const char* tfft_status_string(int s) {
+    switch (s) {
+        case TFFT_OK: return "ok";
+        case TFFT_ERR_BAD_ARG: return "bad argument";
+        case TFFT_ERR_UNSUPPORTED: return "unsupported size or mode (no parameter row or no compiled kernel)";
+        case TFFT_ERR_CUDA: return "CUDA error";
+        case TFFT_ERR_PARAM_FILE: return "parameter CSV missing or malformed";
+        case TFFT_ERR_ALLOC: return "allocation failed";
+        case TFFT_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        default: return "unknown status";
+    }
+}
+
+long long tfft_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"
+
+namespace tfft {
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace tfft

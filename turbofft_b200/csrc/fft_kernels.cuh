@@ -1,0 +1,481 @@
+// Batched power-of-two complex FFT kernels for sm_100a (B200).
+//
+// One kernel template covers every launch of a 1-, 2- or 3-launch split of a
+// 2^logN transform.  It plays the part of the reference's generated
+// fft_radix_2<T, logN, launch, if_ft, if_err> family
+// (include/TurboFFT_radix_2_template.h:1-3, emitted by
+// include/code_gen/scripts/fft_codegen.py:198-504) but shares no structure with
+// it: butterflies are radix-2^LOGE (up to 32) on registers, the in-block data
+// exchange is a Stockham autosort through shared memory, twiddles come from
+// correctly rounded tables, and all index arithmetic is 64-bit.
+//
+// A launch transforms "lines" of length M = 2^LOGM.  A tile is C = 2^LOGC lines
+// that are adjacent in memory in the way the role needs:
+//   ROLE_SINGLE  whole signals, contiguous in and out (1-launch plans)
+//   ROLE_FIRST   lines strided by B = 2^log_b, the C lines of a tile are C
+//                adjacent columns; result goes back to the same positions and is
+//                multiplied by the inter-launch twiddle W_{M*B}^{col*k}
+//                (first and middle launches; fft_codegen.py:385-400)
+//   ROLE_LAST    contiguous lines in, digit-reversed (transposed) store so that
+//                the final order is natural (fft_codegen.py:143-148); the C
+//                lines of a tile are C consecutive values of the slowest digit,
+//                which makes the strided store run over C adjacent addresses.
+//
+// Fault tolerance (FT_DETECT / FT_CORRECT) folds the two-sided checksum of the
+// reference into the same pass (fft_codegen.py:359-384, 432-503, 149-193):
+// left side  sum_p fold(x_p * c_p) with c = W_M r taken while loading,
+// right side sum_k fold(y_k * r_{k mod 3}) taken before the store,
+// and a copy weighted by the 1-based tile counter that locates the tile.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace tfft {
+
+enum { ROLE_SINGLE = 0, ROLE_FIRST = 1, ROLE_LAST = 2 };
+enum { FT_OFF = 0, FT_DETECT = 1, FT_CORRECT = 2 };
+
+template <typename T> struct Cplx;
+template <> struct Cplx<float> { typedef float2 type; };
+template <> struct Cplx<double> { typedef double2 type; };
+
+template <typename T>
+struct KernelArgs {
+    typedef typename Cplx<T>::type C;
+    const C* in;
+    C* out;
+    const C* tw_m;   // W_M^j, j < M            (in-block stage twiddles)
+    const C* tw_lo;  // W_P^j, j < 2^tw_lo_bits (inter-launch twiddle, low part)
+    const C* tw_hi;  // W_P^(j << tw_lo_bits)   (high part), P = M * B
+    const C* cks;    // c = W_M r, M entries    (FT only)
+    long long n_tiles;
+    long long n_lines;  // ROLE_SINGLE: number of signals (ragged last tile)
+    int tiles_per_cta;  // the reference's thread_bs
+    int log_n;          // log2 of the whole transform
+    int log_b;          // ROLE_FIRST: log2 of the line stride
+    int log_n1;         // ROLE_LAST: log2 of the slowest digit's extent
+    int log_q;          // ROLE_LAST: log2 of the middle digit's extent (0 for 2 launches)
+    int tw_lo_bits;
+    int inj_on;         // add err_inj to one element of one tile per selected block
+    int inj_period;     // blocks b with b % inj_period == inj_phase are hit
+    int inj_phase;
+    T err_inj;
+    T err_smoothing;
+    T err_threshold;
+    int* ft_located;          // per block: located tile iteration (1-based) or -1
+    unsigned int* ft_count;   // [0] blocks that detected, [1] tiles recomputed
+    T* ft_diag;               // per block: delta, S, delta_w (may be null)
+};
+
+// ---------------------------------------------------------------- complex helpers
+template <typename C> __device__ __forceinline__ C cadd(C a, C b) { C r; r.x = a.x + b.x; r.y = a.y + b.y; return r; }
+template <typename C> __device__ __forceinline__ C csub(C a, C b) { C r; r.x = a.x - b.x; r.y = a.y - b.y; return r; }
+template <typename C> __device__ __forceinline__ C cmul(C a, C b) {
+    C r;
+    r.x = a.x * b.x - a.y * b.y;
+    r.y = a.x * b.y + a.y * b.x;
+    return r;
+}
+
+// cos(2*pi*k/32), k = 0..8
+template <typename T> __device__ __forceinline__ constexpr T cos32_tab(int k) {
+    return k == 0 ? T(1.0)
+         : k == 1 ? T(0.98078528040323044912618223613424)
+         : k == 2 ? T(0.92387953251128675612818318939679)
+         : k == 3 ? T(0.83146961230254523707878837761791)
+         : k == 4 ? T(0.70710678118654752440084436210485)
+         : k == 5 ? T(0.55557023301960222474283081394853)
+         : k == 6 ? T(0.38268343236508977172845998403040)
+         : k == 7 ? T(0.19509032201612826784828486847702)
+                  : T(0.0);
+}
+// cos and sin of 2*pi*k/32 for 0 <= k <= 16
+template <typename T> __device__ __forceinline__ constexpr T cos32(int k) { return k <= 8 ? cos32_tab<T>(k) : -cos32_tab<T>(16 - k); }
+template <typename T> __device__ __forceinline__ constexpr T sin32(int k) { return k <= 8 ? cos32_tab<T>(8 - k) : cos32_tab<T>(k - 8); }
+
+template <int LR> __device__ __forceinline__ constexpr int brev(int q) {
+    int r = 0;
+    for (int i = 0; i < LR; ++i) r |= ((q >> i) & 1) << (LR - 1 - i);
+    return r;
+}
+
+__device__ __forceinline__ constexpr int ilog2(int x) {
+    int l = 0;
+    while (x > 1) {
+        x >>= 1;
+        ++l;
+    }
+    return l;
+}
+
+// In-register radix-R decimation-in-frequency FFT over v[u + j*STR], j < R.
+// X[q] is left at v[u + brev(q)*STR].  Every index is a compile-time constant
+// once the loops are unrolled, so v stays in registers.
+template <int LR, int LH, int STR, typename T, typename C, int E>
+__device__ __forceinline__ void dif_level(C (&v)[E], const int u) {
+    constexpr int R = 1 << LR;
+    constexpr int half = 1 << LH;
+#pragma unroll
+    for (int t = 0; t < R / 2; ++t) {
+        const int j = t & (half - 1);
+        const int blk = (t >> LH) << (LH + 1);
+        const int ia = u + (blk + j) * STR;
+        const int ib = ia + half * STR;
+        const C a = v[ia];
+        const C b = v[ib];
+        v[ia] = cadd(a, b);
+        const C d = csub(a, b);
+        // multiply by W_{2*half}^j = exp(-2*pi*i*j/(2*half)); angle index in 32nds of a turn
+        const int k32 = j * (16 >> LH);
+        C w;
+        if (k32 == 0) {
+            w = d;
+        } else if (k32 == 8) {  // -i
+            w.x = d.y;
+            w.y = -d.x;
+        } else if (k32 == 4) {  // (1 - i)/sqrt2
+            const T h = cos32_tab<T>(4);
+            w.x = (d.x + d.y) * h;
+            w.y = (d.y - d.x) * h;
+        } else if (k32 == 12) {  // (-1 - i)/sqrt2
+            const T h = cos32_tab<T>(4);
+            w.x = (d.y - d.x) * h;
+            w.y = -(d.x + d.y) * h;
+        } else {
+            const T wr = cos32<T>(k32);
+            const T wi = -sin32<T>(k32);
+            w.x = d.x * wr - d.y * wi;
+            w.y = d.x * wi + d.y * wr;
+        }
+        v[ib] = w;
+    }
+    if constexpr (LH > 0) dif_level<LR, LH - 1, STR, T>(v, u);
+}
+
+template <int LR, int STR, typename T, typename C, int E>
+__device__ __forceinline__ void dif_butterfly(C (&v)[E], const int u) {
+    if constexpr (LR > 0) dif_level<LR, LR - 1, STR, T>(v, u);
+}
+
+// ---------------------------------------------------------------- configuration
+template <typename T, int LOGM, int LOGE, int LOGC, int ROLE>
+struct Cfg {
+    static_assert(LOGE >= 1 && LOGE <= 5, "elements per thread: 2..32");
+    static_assert(LOGE <= LOGM, "a thread cannot hold more than a line");
+    static constexpr int M = 1 << LOGM;
+    static constexpr int E = 1 << LOGE;
+    static constexpr int C = 1 << LOGC;
+    static constexpr int LOGTPL = LOGM - LOGE;  // threads per line
+    static constexpr int TPL = 1 << LOGTPL;
+    static constexpr int THREADS = TPL * C;
+    static constexpr int S = (LOGM + LOGE - 1) / LOGE;  // register stages
+    static constexpr int LOGR0 = LOGM - (S - 1) * LOGE; // first stage takes the remainder
+    static_assert(ROLE != ROLE_LAST || S >= 2, "transposed store needs one exchange");
+    static constexpr bool CFAST_IN = (ROLE == ROLE_FIRST);
+    static constexpr bool CFAST_OUT = (ROLE != ROLE_SINGLE);
+    static constexpr bool LAYOUT_COLS = (ROLE == ROLE_FIRST);
+    static constexpr int BANKW = 128 / (2 * (int)sizeof(T));  // complex elements per 128 B
+    static constexpr int PADSHIFT = sizeof(T) == 4 ? 4 : 3;
+    static constexpr int MPAD = M + (M >> PADSHIFT);
+    static constexpr int PITCH =
+        ROLE == ROLE_LAST ? (MPAD | 1)
+        : (TPL >= BANKW ? MPAD : ((MPAD + BANKW - 1) / BANKW) * BANKW + TPL);
+    static constexpr int SMEM_ELEMS = S > 1 ? (LAYOUT_COLS ? M * C : PITCH * C) : 0;
+    static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
+};
+
+template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
+struct Fft {
+    typedef Cfg<T, LOGM, LOGE, LOGC, ROLE> K;
+    typedef typename Cplx<T>::type C;
+    static constexpr int E = K::E;
+    static constexpr int TPL = K::TPL;
+
+    struct Geom {
+        long long in_base, out_base, in_rs, in_cs, out_rs, out_cs, col0;
+        int ncols;
+    };
+
+    // per-thread FT state that lives across the tiles of a block
+    struct FtRegs {
+        T ca[E], cb[E];  // fold weights of the left checksum: c.x + c.y, c.x - c.y
+        T al[3], be[3];  // fold weights of the right checksum, rotated by s mod 3
+    };
+
+    template <int ST> static __device__ __forceinline__ constexpr int logR() { return ST == 0 ? K::LOGR0 : LOGE; }
+    template <int ST> static __device__ __forceinline__ constexpr int logP() { return ST == 0 ? 0 : K::LOGR0 + (ST - 1) * LOGE; }
+
+    template <bool CF> static __device__ __forceinline__ void map_thread(int& s, int& c) {
+        const int tid = threadIdx.x;
+        if (CF) {
+            c = tid & (K::C - 1);
+            s = tid >> LOGC;
+        } else {
+            s = tid & (TPL - 1);
+            c = tid >> K::LOGTPL;
+        }
+    }
+
+    static __device__ __forceinline__ int soff(int a, int c) {
+        if (K::LAYOUT_COLS) return a * K::C + c;
+        return c * K::PITCH + a + (a >> K::PADSHIFT);
+    }
+
+    static __device__ __forceinline__ Geom decode(const KernelArgs<T>& a, long long tile) {
+        Geom g;
+        if (ROLE == ROLE_SINGLE) {
+            const long long line0 = tile << LOGC;
+            g.in_base = g.out_base = line0 << LOGM;
+            g.in_rs = g.out_rs = 1;
+            g.in_cs = g.out_cs = K::M;
+            const long long left = a.n_lines - line0;
+            g.ncols = left < K::C ? (int)left : K::C;
+            g.col0 = 0;
+        } else if (ROLE == ROLE_FIRST) {
+            const int ltpo = a.log_b - LOGC;  // log2 tiles per outer index
+            const long long o = tile >> ltpo;
+            const long long b0 = (tile & ((1LL << ltpo) - 1)) << LOGC;
+            g.in_base = g.out_base = (o << (LOGM + a.log_b)) + b0;
+            g.in_rs = g.out_rs = 1LL << a.log_b;
+            g.in_cs = g.out_cs = 1;
+            g.ncols = K::C;
+            g.col0 = b0;
+        } else {
+            const int lk = a.log_n1 - LOGC;
+            const long long batch = tile >> (lk + a.log_q);
+            const long long t = tile & ((1LL << (lk + a.log_q)) - 1);
+            const long long k10 = (t & ((1LL << lk) - 1)) << LOGC;
+            const long long k2 = t >> lk;
+            g.in_base = (batch << a.log_n) + (((k10 << a.log_q) + k2) << LOGM);
+            g.in_rs = 1;
+            g.in_cs = 1LL << (a.log_q + LOGM);
+            g.out_base = (batch << a.log_n) + k10 + (k2 << a.log_n1);
+            g.out_rs = 1LL << (a.log_n1 + a.log_q);
+            g.out_cs = 1;
+            g.ncols = K::C;
+            g.col0 = 0;
+        }
+        return g;
+    }
+
+    // Final stage: natural-order outputs, right checksum, inter-launch twiddle, store.
+    template <int LR, bool DO_FT>
+    static __device__ __forceinline__ void finish(C (&v)[E], const KernelArgs<T>& a, const Geom& g, int s, int c,
+                                                  const FtRegs& f, T& tout) {
+        constexpr int R = 1 << LR, NB = E / R;
+        C y[E];
+#pragma unroll
+        for (int u = 0; u < NB; ++u)
+#pragma unroll
+            for (int q = 0; q < R; ++q) y[u + q * NB] = v[u + brev<LR>(q) * NB];
+        if (DO_FT) {
+            constexpr int t3 = (K::LOGTPL & 1) ? 2 : 1;  // TPL mod 3
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                const int cls = (i * t3) % 3;
+                tout = fma(y[i].x, f.al[cls], tout);
+                tout = fma(y[i].y, f.be[cls], tout);
+            }
+        }
+        if (ROLE == ROLE_FIRST) {
+            // y_k *= W_P^{col*k}, k = s + i*TPL: base * step^i with a log-depth power tree
+            const unsigned long long col = (unsigned long long)(g.col0 + c);
+            const unsigned long long pmask = (1ULL << (LOGM + a.log_b)) - 1;
+            const unsigned long long lomask = (1ULL << a.tw_lo_bits) - 1;
+            const unsigned long long jb = (col * (unsigned long long)s) & pmask;
+            const unsigned long long js = (col * (unsigned long long)TPL) & pmask;
+            C w[E], pw[LOGE];
+            w[0] = cmul(__ldg(a.tw_lo + (jb & lomask)), __ldg(a.tw_hi + (jb >> a.tw_lo_bits)));
+            pw[0] = cmul(__ldg(a.tw_lo + (js & lomask)), __ldg(a.tw_hi + (js >> a.tw_lo_bits)));
+#pragma unroll
+            for (int l = 1; l < LOGE; ++l) pw[l] = cmul(pw[l - 1], pw[l - 1]);
+#pragma unroll
+            for (int i = 1; i < E; ++i) w[i] = cmul(w[i - (1 << ilog2(i))], pw[ilog2(i)]);
+#pragma unroll
+            for (int i = 0; i < E; ++i) y[i] = cmul(y[i], w[i]);
+        }
+        if (c < g.ncols) {
+            C* dst = a.out + g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
+#pragma unroll
+            for (int i = 0; i < E; ++i) dst[(long long)i * TPL * g.out_rs] = y[i];
+        }
+    }
+
+    template <int ST, bool DO_FT>
+    static __device__ __forceinline__ void stage(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g,
+                                                 const FtRegs& f, T& tout) {
+        constexpr int LR = logR<ST>(), R = 1 << LR, LP = logP<ST>(), P = 1 << LP, NB = E / R;
+        constexpr bool LASTST = (ST == K::S - 1);
+        constexpr bool CF = LASTST ? K::CFAST_OUT : K::CFAST_IN;
+        int s, c;
+        map_thread<CF>(s, c);
+        if (ST > 0) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = sm[soff(s + i * TPL, c)];
+            __syncthreads();  // everybody has read before anybody overwrites
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u) dif_butterfly<LR, NB, T>(v, u);
+        if constexpr (!LASTST) {
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int b = s + u * TPL;
+                const int p = b & (P - 1);
+                const int nlo = b >> LP;
+                const int abase = p + (nlo << (LP + LR));
+#pragma unroll
+                for (int q = 0; q < R; ++q) {
+                    C val = v[u + brev<LR>(q) * NB];
+                    if (q > 0) val = cmul(val, __ldg(a.tw_m + ((nlo * q) << LP)));
+                    sm[soff(abase + (q << LP), c)] = val;
+                }
+            }
+            __syncthreads();
+            stage<ST + 1, DO_FT>(v, sm, a, g, f, tout);
+        } else {
+            finish<LR, DO_FT>(v, a, g, s, c, f, tout);
+        }
+    }
+
+    // One tile: load, all stages, store.  tin/tout receive this thread's share of the
+    // tile's left and right checksums.
+    template <bool DO_FT, bool DO_INJ>
+    static __device__ __forceinline__ void tile(const KernelArgs<T>& a, C* sm, long long tile_id, bool inject,
+                                                const FtRegs& f, T& tin, T& tout) {
+        const Geom g = decode(a, tile_id);
+        int s, c;
+        map_thread<K::CFAST_IN>(s, c);
+        C v[E];
+        if (c < g.ncols) {
+            const C* src = a.in + g.in_base + (long long)c * g.in_cs + (long long)s * g.in_rs;
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = src[(long long)i * TPL * g.in_rs];
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
+        }
+        if (DO_FT) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                tin = fma(v[i].x, f.ca[i], tin);
+                tin = fma(v[i].y, f.cb[i], tin);
+            }
+        }
+        if (DO_INJ) {
+            if (inject && threadIdx.x == 0) v[0].x += a.err_inj;
+        }
+        stage<0, DO_FT>(v, sm, a, g, f, tout);
+    }
+
+    static __device__ __forceinline__ T warp_sum(T x) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        return x;
+    }
+
+    static __device__ __forceinline__ void run(const KernelArgs<T>& a, C* sm) {
+        const long long grid = gridDim.x;
+        if (FT == FT_OFF) {
+            FtRegs f;
+            T tin = 0, tout = 0;
+            for (int it = 0; it < a.tiles_per_cta; ++it) {
+                const long long t = blockIdx.x + it * grid;
+                if (t >= a.n_tiles) break;
+                tile<false, false>(a, sm, t, false, f, tin, tout);
+            }
+            return;
+        }
+        // ---- FT: checksum weights
+        FtRegs f;
+        {
+            int s, c;
+            map_thread<K::CFAST_IN>(s, c);
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                const C cc = __ldg(a.cks + s + i * TPL);
+                f.ca[i] = cc.x + cc.y;
+                f.cb[i] = cc.x - cc.y;
+            }
+            map_thread<K::CFAST_OUT>(s, c);
+            // r_j = omega^j with the float32-rounded imaginary part of the reference
+            // (include/turbofft/constants.h:2-7)
+            const T h = T(0.8660253882408142);
+            const T alpha[3] = {T(1), T(-0.5) - h, T(-0.5) + h};
+            const T beta[3] = {T(1), T(-0.5) + h, T(-0.5) - h};
+            const int s3 = s % 3;
+#pragma unroll
+            for (int t = 0; t < 3; ++t) {
+                const int j = (s3 + t) % 3;
+                f.al[t] = j == 0 ? alpha[0] : (j == 1 ? alpha[1] : alpha[2]);
+                f.be[t] = j == 0 ? beta[0] : (j == 1 ? beta[1] : beta[2]);
+            }
+        }
+        const bool hit = a.inj_on && ((int)(blockIdx.x % (unsigned)a.inj_period) == a.inj_phase);
+        const int inj_it = (int)((blockIdx.x / (unsigned)a.inj_period) % (unsigned)a.tiles_per_cta);
+        T acc_in = 0, acc_out = 0, acc_w = 0;
+        int done = 0;
+        for (int it = 0; it < a.tiles_per_cta; ++it) {
+            const long long t = blockIdx.x + it * grid;
+            if (t >= a.n_tiles) break;
+            T tin = 0, tout = 0;
+            tile<true, true>(a, sm, t, hit && it == inj_it, f, tin, tout);
+            acc_in += tin;
+            acc_out += tout;
+            acc_w = fma(T(it + 1), tin - tout, acc_w);
+            ++done;
+        }
+        // ---- block decision (fft_codegen.py:432-503)
+        __shared__ T red[3][32];
+        __shared__ int s_k;
+        T delta = warp_sum(acc_in - acc_out);
+        T mag = warp_sum(fabs(acc_in) + fabs(acc_out));
+        T dw = warp_sum(acc_w);
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        constexpr int NW = (K::THREADS + 31) / 32;
+        if (lane == 0) {
+            red[0][wid] = delta;
+            red[1][wid] = mag;
+            red[2][wid] = dw;
+        }
+        __syncthreads();
+        if (wid == 0) {
+            delta = lane < NW ? red[0][lane] : T(0);
+            mag = lane < NW ? red[1][lane] : T(0);
+            dw = lane < NW ? red[2][lane] : T(0);
+            delta = warp_sum(delta);
+            mag = warp_sum(mag);
+            dw = warp_sum(dw);
+            if (lane == 0) {
+                int k = -1;
+                if (fabs(delta) / (a.err_smoothing + fabs(mag)) > a.err_threshold) k = (int)round(fabs(dw) / fabs(delta));
+                s_k = k;
+                a.ft_located[blockIdx.x] = k;
+                if (k != -1) atomicAdd(a.ft_count, 1u);
+                if (a.ft_diag) {
+                    a.ft_diag[3 * (long long)blockIdx.x + 0] = delta;
+                    a.ft_diag[3 * (long long)blockIdx.x + 1] = mag;
+                    a.ft_diag[3 * (long long)blockIdx.x + 2] = dw;
+                }
+            }
+        }
+        __syncthreads();
+        if (FT == FT_CORRECT) {
+            // recompute the located tile from the untouched input (fft_codegen.py:149-193)
+            const int k = s_k;
+            if (k >= 1 && k <= done) {
+                T tin = 0, tout = 0;
+                tile<false, false>(a, sm, blockIdx.x + (long long)(k - 1) * grid, false, f, tin, tout);
+                if (threadIdx.x == 0) atomicAdd(a.ft_count + 1, 1u);
+            }
+        }
+    }
+};
+
+template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
+__global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS))
+fft_kernel(const __grid_constant__ KernelArgs<T> a) {
+    extern __shared__ __align__(16) unsigned char tfft_smem_raw[];
+    typedef typename Cplx<T>::type C;
+    Fft<T, LOGM, LOGE, LOGC, ROLE, FT>::run(a, reinterpret_cast<C*>(tfft_smem_raw));
+}
+
+}  // namespace tfft

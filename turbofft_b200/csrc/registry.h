@@ -1,0 +1,24 @@
+// Kernel table: the B200 counterpart of TurboFFT_Kernel_Entry<...>::turboFFTArr[26][3]
+// (include/TurboFFT.h:22-25).  Instead of one pointer per (logN, launch) the table is
+// keyed by what a launch does -- (dtype, role, log2 line length, log2 points per thread,
+// log2 lines per tile, FT mode) -- so that any parameter row whose launches are compiled
+// can be planned at run time.
+#pragma once
+#include <cstddef>
+
+namespace tfft {
+
+struct KernelEntry {
+    const void* fn[3];  // FT_OFF, FT_DETECT, FT_CORRECT (null = not compiled)
+    int threads;
+    size_t smem;
+};
+
+void register_kernel(int dtype, int role, int logm, int loge, int logc, int ft, const void* fn, int threads,
+                     size_t smem);
+const KernelEntry* find_kernel(int dtype, int role, int logm, int loge, int logc);
+int registered_kernel_count();
+// counts one kernel launch of this library (see tfft_launch_count)
+void note_launch();
+
+}  // namespace tfft
