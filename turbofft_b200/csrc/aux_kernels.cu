@@ -8,19 +8,17 @@
 
 namespace {
 
+// Each block copies one contiguous chunk of 2 x 256 x 16 bytes and exits; on B200 a
+// full grid of short blocks measured higher than a persistent grid-stride loop.
 __global__ void __launch_bounds__(256) stream_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                           size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    // four independent 128-bit loads in flight per thread
-    for (; i + 3 * stride < n; i += 4 * stride) {
-        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
-        dst[i] = a;
-        dst[i + stride] = b;
-        dst[i + 2 * stride] = c;
-        dst[i + 3 * stride] = d;
-    }
-    for (; i < n; i += stride) dst[i] = src[i];
+    const size_t i0 = (size_t)blockIdx.x * 512 + threadIdx.x;
+    const size_t i1 = i0 + 256;
+    uint4 a, b;
+    if (i0 < n) a = __ldcs(src + i0);
+    if (i1 < n) b = __ldcs(src + i1);
+    if (i0 < n) __stcs(dst + i0, a);
+    if (i1 < n) __stcs(dst + i1, b);
 }
 
 template <typename C> struct RealOf;
@@ -90,12 +88,8 @@ int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream) {
     if (!src || !dst || (bytes & 15) || (((size_t)src | (size_t)dst) & 15)) return TFFT_ERR_BAD_ARG;
     const size_t n = bytes / 16;
     if (n == 0) return TFFT_OK;
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) != cudaSuccess) return TFFT_ERR_CUDA;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    size_t blocks = (n + 255) / 256;
-    const size_t cap = (size_t)sms * 8;  // 2048 threads per SM
-    if (blocks > cap) blocks = cap;
+    const size_t blocks = (n + 511) / 512;
+    if (blocks > 2147483647ULL) return TFFT_ERR_TOO_LARGE;
     stream_copy_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, n);
     tfft::note_launch();
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;

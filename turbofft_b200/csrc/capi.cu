@@ -30,7 +30,7 @@ struct LaunchDesc {
     long long n_lines = 0;
     unsigned grid = 0;
     int log_b = 0, log_n1 = 0, log_q = 0, tw_lo_bits = 0;
-    void* tw_m = nullptr;
+    void* tw_st = nullptr;
     void* tw_lo = nullptr;
     void* tw_hi = nullptr;
     void* cks = nullptr;
@@ -104,6 +104,34 @@ void fill_twiddles(std::vector<C>& v, long long count, long long stride, int log
     }
 }
 
+// Stage twiddles of the in-block Stockham exchange, in the order the kernel reads them
+// (fft_kernels.cuh, KernelArgs::tw_st): for stage t with radix R_t = 2^lr and already
+// transformed extent P_t = 2^lp, entry (q, b) = W_M^{(b >> lp) * q << lp} for q = 1..R_t-1
+// and butterfly b < M / R_t.
+template <typename C>
+void stage_twiddles(std::vector<C>& v, int logm, int loge) {
+    v.clear();
+    const int stages = (logm + loge - 1) / loge;
+    const int logr0 = logm - (stages - 1) * loge;
+    const long double two_pi = 6.283185307179586476925286766559005768L;
+    const long long m = 1LL << logm;
+    for (int t = 0; t + 1 < stages; ++t) {
+        const int lr = t == 0 ? logr0 : loge;
+        const int lp = t == 0 ? 0 : logr0 + (t - 1) * loge;
+        for (long long q = 1; q < (1LL << lr); ++q) {
+            for (long long b = 0; b < (m >> lr); ++b) {
+                const long long idx = (((b >> lp) * q) << lp) & (m - 1);
+                const long double ang = -two_pi * (long double)idx / (long double)m;
+                C w;
+                w.x = (decltype(w.x))cosl(ang);
+                w.y = (decltype(w.y))sinl(ang);
+                v.push_back(w);
+            }
+        }
+    }
+    if (v.empty()) v.resize(1);  // single-stage launches read nothing
+}
+
 // c = W_M r with r_j = omega^(j mod 3): the ABFT encoding vector of
 // getDFTMatrixChecksum() (include/utils/abft.h:21-61), evaluated as the FFT of r in
 // extended precision instead of the reference's O(M^2) float-angle loop.
@@ -151,17 +179,17 @@ bool build_tables(tfft_plan p) {
     typedef typename Cplx<T>::type C;
     for (int i = 0; i < p->n_launch; ++i) {
         LaunchDesc& d = p->L[i];
-        // reuse tables of an earlier launch with the same line length
+        // reuse tables of an earlier launch with the same line length and radix plan
         int same = -1;
         for (int j = 0; j < i; ++j)
-            if (p->L[j].logm == d.logm) same = j;
+            if (p->L[j].logm == d.logm && p->L[j].loge == d.loge) same = j;
         if (same >= 0) {
-            d.tw_m = p->L[same].tw_m;
+            d.tw_st = p->L[same].tw_st;
             d.cks = p->L[same].cks;
         } else {
             std::vector<C> t;
-            fill_twiddles(t, 1LL << d.logm, 1, d.logm);
-            if (!upload(p, t, &d.tw_m)) return false;
+            stage_twiddles(t, d.logm, d.loge);
+            if (!upload(p, t, &d.tw_st)) return false;
             if (p->if_ft) {
                 std::vector<long double> re, im;
                 checksum_vector(d.logm, re, im);
@@ -205,7 +233,7 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         memset(&a, 0, sizeof(a));
         a.in = (const C*)(i == 0 ? in : p->scratch);
         a.out = (C*)(i == p->n_launch - 1 ? out : p->scratch);
-        a.tw_m = (const C*)d.tw_m;
+        a.tw_st = (const C*)d.tw_st;
         a.tw_lo = (const C*)d.tw_lo;
         a.tw_hi = (const C*)d.tw_hi;
         a.cks = (const C*)d.cks;

@@ -43,7 +43,9 @@ struct KernelArgs {
     typedef typename Cplx<T>::type C;
     const C* in;
     C* out;
-    const C* tw_m;   // W_M^j, j < M            (in-block stage twiddles)
+    const C* tw_st;  // in-block stage twiddles, laid out so that a warp reads them coalesced:
+                     // stage t, output q >= 1, butterfly b -> W_M^{(b >> logP_t) * q << logP_t}
+                     // at stage_offset(t) + (q - 1) * (M / R_t) + b
     const C* tw_lo;  // W_P^j, j < 2^tw_lo_bits (inter-launch twiddle, low part)
     const C* tw_hi;  // W_P^(j << tw_lo_bits)   (high part), P = M * B
     const C* cks;    // c = W_M r, M entries    (FT only)
@@ -181,6 +183,13 @@ struct Cfg {
         : (TPL >= BANKW ? MPAD : ((MPAD + BANKW - 1) / BANKW) * BANKW + TPL);
     static constexpr int SMEM_ELEMS = S > 1 ? (LAYOUT_COLS ? M * C : PITCH * C) : 0;
     static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
+    // Occupancy target handed to the compiler as the register cap: enough blocks for
+    // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
+    static constexpr int SMEM_BLOCKS = SMEM_BYTES ? (int)((220 * 1024) / SMEM_BYTES) : 32;
+    static constexpr int THREAD_BLOCKS = (sizeof(T) == 4 ? 1024 : 512) / THREADS;
+    static constexpr int MIN_BLOCKS =
+        (SMEM_BLOCKS < THREAD_BLOCKS ? SMEM_BLOCKS : THREAD_BLOCKS) < 1 ? 1
+        : (SMEM_BLOCKS < THREAD_BLOCKS ? SMEM_BLOCKS : THREAD_BLOCKS);
 };
 
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
@@ -203,6 +212,15 @@ struct Fft {
 
     template <int ST> static __device__ __forceinline__ constexpr int logR() { return ST == 0 ? K::LOGR0 : LOGE; }
     template <int ST> static __device__ __forceinline__ constexpr int logP() { return ST == 0 ? 0 : K::LOGR0 + (ST - 1) * LOGE; }
+    // first entry of stage ST in the stage-twiddle table: sum over earlier stages of (R - 1) * M / R
+    template <int ST> static __device__ __forceinline__ constexpr int twOff() {
+        int off = 0;
+        for (int t = 0; t < ST; ++t) {
+            const int lr = t == 0 ? K::LOGR0 : LOGE;
+            off += ((1 << lr) - 1) << (LOGM - lr);
+        }
+        return off;
+    }
 
     template <bool CF> static __device__ __forceinline__ void map_thread(int& s, int& c) {
         const int tid = threadIdx.x;
@@ -215,9 +233,16 @@ struct Fft {
         }
     }
 
+    // Shared-memory position of Stockham address a of line c.  Row layout pads one
+    // element per 2^PADSHIFT.  soff(x + y, c) == soff(x, c) + sdelta(y) whenever x and y
+    // occupy disjoint bit fields, which lets every unrolled access use a constant offset
+    // from one per-thread base.
     static __device__ __forceinline__ int soff(int a, int c) {
         if (K::LAYOUT_COLS) return a * K::C + c;
         return c * K::PITCH + a + (a >> K::PADSHIFT);
+    }
+    static __device__ __forceinline__ constexpr int sdelta(int y) {
+        return K::LAYOUT_COLS ? y * K::C : y + (y >> K::PADSHIFT);
     }
 
     static __device__ __forceinline__ Geom decode(const KernelArgs<T>& a, long long tile) {
@@ -309,8 +334,11 @@ struct Fft {
         int s, c;
         map_thread<CF>(s, c);
         if (ST > 0) {
+            {
+                const C* rd = sm + soff(s, c);  // s < TPL and i * TPL share no bits
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = sm[soff(s + i * TPL, c)];
+                for (int i = 0; i < E; ++i) v[i] = rd[sdelta(i * TPL)];
+            }
             __syncthreads();  // everybody has read before anybody overwrites
         }
 #pragma unroll
@@ -321,12 +349,14 @@ struct Fft {
                 const int b = s + u * TPL;
                 const int p = b & (P - 1);
                 const int nlo = b >> LP;
-                const int abase = p + (nlo << (LP + LR));
+                // p, q << LP and nlo << (LP + LR) are disjoint bit fields of the address
+                C* wr = sm + soff(p + (nlo << (LP + LR)), c);
+                const C* tw = a.tw_st + twOff<ST>() + b;
 #pragma unroll
                 for (int q = 0; q < R; ++q) {
                     C val = v[u + brev<LR>(q) * NB];
-                    if (q > 0) val = cmul(val, __ldg(a.tw_m + ((nlo * q) << LP)));
-                    sm[soff(abase + (q << LP), c)] = val;
+                    if (q > 0) val = cmul(val, __ldg(tw + (q - 1) * (K::M / R)));
+                    wr[sdelta(q << LP)] = val;
                 }
             }
             __syncthreads();
@@ -471,7 +501,7 @@ struct Fft {
 };
 
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
-__global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS))
+__global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS), (Cfg<T, LOGM, LOGE, LOGC, ROLE>::MIN_BLOCKS))
 fft_kernel(const __grid_constant__ KernelArgs<T> a) {
     extern __shared__ __align__(16) unsigned char tfft_smem_raw[];
     typedef typename Cplx<T>::type C;
