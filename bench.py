@@ -1,0 +1,412 @@
+#!/usr/bin/env python3
+"""Benchmark of the batched C2C FFT hot path: the logN + logBS = 28 sweep.
+
+One step = one pass over the reference's `--if_bench 2` shape (main.cu:117-127):
+for logN = lo..hi, a forward FFT of batch = 2^(log_total - logN) signals of length 2^logN.
+Metric = GFLOPS with the reference's formula 5*N*log2(N)*batch / t (main.cu:68), summed
+over the sweep; HBM GB/s uses the reference's algorithmic bytes 2*N*batch*sizeof(T)
+(main.cu:69).  Prints ONE JSON line (see README / DESIGN for the keys).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--datatype 0|1] [--ft 0|1|2] [--thread_bs B] [--lo 7] [--hi 24]
+                  [--log-total 28] [--cufft] [--no-e2e] [--no-cpu]
+
+N > 1 is launched with torch.distributed.run, one rank per GPU; the batch is sharded
+(every rank transforms its own 2^log_total elements per point, no data-path collective).
+--impl reference times the CPU port of the same sweep on the host cores (the reference
+has no CPU implementation; see oracle/cpu_fft.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "c2c_fft_gflops_logN_plus_logBS_28_sweep"
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--datatype", type=int, default=0, help="0 float2 (complex64), 1 double2 (complex128)")
+    ap.add_argument("--ft", type=int, default=0, help="0 off, 1 detect (--if_ft), 2 inject+correct (--if_err)")
+    ap.add_argument("--thread_bs", type=int, default=1)
+    ap.add_argument("--lo", type=int, default=7)
+    ap.add_argument("--hi", type=int, default=24)
+    ap.add_argument("--log-total", type=int, default=28)
+    ap.add_argument("--cufft", action="store_true", help="also time cuFFT on the same buffers (comparison only)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-log-sample", type=int, default=24, help="log2 elements per sweep point in the CPU sample")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def workload_name(a):
+    dt = "complex64 uniform[-1,1)" if a.datatype == 0 else "complex128 N(0,1)"
+    ft = {0: "FT off", 1: "FT detect", 2: "FT inject+correct"}[a.ft]
+    return (f"cfg2 sweep: logN={a.lo}..{a.hi}, batch=2^({a.log_total}-logN), {dt}, forward unnormalised, {ft}"
+            if a.datatype == 0 else
+            f"cfg3 sweep: logN={a.lo}..{a.hi}, batch=2^({a.log_total}-logN), {dt}, forward unnormalised, {ft}")
+
+
+def flops_of_point(logn, log_total):
+    return 5.0 * (1 << log_total) * logn
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+
+def make_host_input(n_complex, datatype, seed):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    if datatype == 0:
+        return rng.uniform(-1.0, 1.0, size=2 * n_complex).astype(np.float32).view(np.complex64)
+    return rng.standard_normal(size=2 * n_complex).view(np.complex128)
+
+
+def cpu_sweep(a, reps=1):
+    """Times the CPU port on a bounded sample: 2^cpu_log_sample elements per sweep point."""
+    from oracle import cpu_fft
+
+    workers = cpu_fft.host_threads()
+    ls = min(a.cpu_log_sample, a.log_total)
+    x = make_host_input(1 << ls, a.datatype, 1)
+    total_t, total_f, per = 0.0, 0.0, []
+    for logn in range(a.lo, a.hi + 1):
+        if logn > ls:
+            continue
+        xs = x.reshape(1 << (ls - logn), 1 << logn)
+        best = None
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            cpu_fft.cpu_fft(xs, workers)
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        total_t += best
+        total_f += 5.0 * (1 << ls) * logn
+        per.append((logn, best))
+    return total_f / total_t / 1e9, total_t, workers, ls, per
+
+
+def run_reference(a):
+    """Reference arm: the CPU port of the path, all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    for _ in range(max(0, a.warmup)):
+        cpu_sweep(a)
+    t_all, f_all = 0.0, 0.0
+    for _ in range(a.steps):
+        gf, t, workers, ls, _ = cpu_sweep(a)
+        t_all += t
+        f_all += gf * t
+    value = f_all / t_all
+    sample = (f"2^{ls} elements per sweep point (1/{1 << (a.log_total - ls)} of the workload's batch), "
+              f"scipy.fft (pocketfft) with {workers} threads; GFLOPS is size-independent under batch scaling")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GFLOPS", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": 1e3 * t_all / a.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32" if a.datatype == 0 else "f64", "data": "synthetic",
+        "config": {"workload": workload_name(a), "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GFLOPS", "cores": workers, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships no CPU implementation of the transform; this is a CPU port (pocketfft)",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only)."""
+
+    def __init__(self, uuid, index, period=0.1):
+        super().__init__(daemon=True)
+        self.period = period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.ok:
+            self.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+
+def run_ours(a):
+    import ctypes as C
+
+    import torch
+
+    import turbofft_b200 as tf
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the FFT has no CPU path (use --impl reference for the CPU port)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    tf.lib()  # fails loudly if the CUDA library is missing
+
+    tdtype = torch.complex64 if a.datatype == 0 else torch.complex128
+    esize = 8 if a.datatype == 0 else 16
+    n = 1 << a.log_total
+    points = list(range(a.lo, a.hi + 1))
+    alg_bytes_point = 2.0 * n * esize
+
+    # seeded synthetic input, generated on the host (pinned) and copied once
+    host_np = make_host_input(n, a.datatype, seed=rank)
+    host_in = torch.from_numpy(host_np).pin_memory()
+    x = host_in.to(dev, non_blocking=True)
+    y = torch.empty_like(x)
+    torch.cuda.synchronize()
+
+    plans = {}
+    for logn in points:
+        plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2),
+                              thread_bs=a.thread_bs, device=local)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step(events=None):
+        for i, logn in enumerate(points):
+            plans[logn].exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+            if events is not None:
+                events[i + 1].record()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # same-run STREAM-copy peak
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        tf.stream_copy(x, y)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(10):
+        tf.stream_copy(x, y)
+    ev1.record()
+    torch.cuda.synchronize()
+    copy_gbs = 2.0 * n * esize * 10 / (ev0.elapsed_time(ev1) * 1e-3) / 1e9
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    barrier()
+
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(uuid, local)
+    if sampler.ok:
+        sampler.start()
+
+    # ---- timed region: K steps, device-timed, per-point events
+    launches0 = tf.launch_count()
+    all_events = [[torch.cuda.Event(enable_timing=True) for _ in range(len(points) + 1)] for _ in range(a.steps)]
+    barrier()
+    for k in range(a.steps):
+        all_events[k][0].record()
+        step(all_events[k])
+    barrier()
+    launches = tf.launch_count() - launches0
+    total_ms = sum(ev[0].elapsed_time(ev[-1]) for ev in all_events)
+    clocks = sampler.stop() if sampler.ok else {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+    t_local = total_ms / a.steps
+    if dist is not None:
+        t = torch.tensor([t_local], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_step = float(t.item())
+    else:
+        t_step = t_local
+
+    flops_step = sum(flops_of_point(l, a.log_total) for l in points)
+    value = world * flops_step / (t_step * 1e-3) / 1e9
+    per_point = []
+    for i, logn in enumerate(points):
+        ms = sum(ev[i].elapsed_time(ev[i + 1]) for ev in all_events) / a.steps
+        per_point.append({"logN": logn, "ms": round(ms, 4), "gflops": round(flops_of_point(logn, a.log_total) / ms / 1e6, 1),
+                          "gbs": round(alg_bytes_point / ms / 1e6, 1), "launches": len(plans[logn].info())})
+
+    # ---- property check on the last point's output (no oracle here): Parseval
+    logn_chk = points[-1]
+    plans[logn_chk].exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+    torch.cuda.synchronize()
+    ex = float((x.real.double() ** 2 + x.imag.double() ** 2).sum().item())
+    ey = float((y.real.double() ** 2 + y.imag.double() ** 2).sum().item())
+    parseval = abs(ey / ((1 << logn_chk) * ex) - 1.0)
+
+    ft_info = None
+    if a.ft:
+        nd, nc, loc = plans[logn_chk].ft_status()
+        ft_info = {"logN": logn_chk, "blocks": len(loc), "detected": nd, "corrected": nc}
+
+    # ---- optional cuFFT column (comparison only, separate library)
+    cufft = None
+    if a.cufft and rank == 0:
+        cmp = C.CDLL(os.path.join(os.path.dirname(tf.__file__), "libturbofft_cufft_cmp.so"))
+        cmp.tfft_cmp_cufft.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                       C.POINTER(C.c_float), C.c_void_p]
+        cufft, tot = [], 0.0
+        for logn in points:
+            ms = C.c_float(0)
+            rc = cmp.tfft_cmp_cufft(logn, 1 << (a.log_total - logn), a.datatype, x.data_ptr(), y.data_ptr(), 5,
+                                    C.byref(ms), stream)
+            cufft.append({"logN": logn, "ms": round(ms.value, 4) if rc == 0 else None})
+            tot += ms.value if rc == 0 else float("nan")
+        cufft = {"gflops": flops_step / tot / 1e6, "ms_per_step": tot, "per_point": cufft}
+
+    # ---- end to end through the public host-buffer API (tfft_exec_host)
+    e2e = None
+    if not a.no_e2e:
+        host_out = torch.empty_like(host_in).pin_memory()
+        for logn in points[:2]:
+            plans[logn].exec_host(host_in, host_out)
+        barrier()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.e2e_steps):
+            for logn in points:
+                plans[logn].exec_host(host_in, host_out)
+        e1.record()
+        torch.cuda.synchronize()
+        e_ms = e0.elapsed_time(e1) / a.e2e_steps
+        if dist is not None:
+            t = torch.tensor([e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        e2e = {"value": world * flops_step / (e_ms * 1e-3) / 1e9, "unit": "GFLOPS",
+               "h2d_bytes_per_step": int(len(points) * n * esize), "d2h_bytes_per_step": int(len(points) * n * esize),
+               "steps": a.e2e_steps, "ms_per_step": e_ms, "api": "tfft_exec_host (pinned host buffers)"}
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    peak, peak_src = peaks()
+    achieved = alg_bytes_point * len(points) / (t_local * 1e-3) / 1e9
+    dominant = max(per_point, key=lambda p: p["ms"])
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "traffic": None,
+        "peak_source": peak_src, "stream_copy_gbs_same_run": copy_gbs, "frac_of_same_run_copy": achieved / copy_gbs,
+        "kernel": "tfft::fft_kernel<T,LOGM,LOGE,LOGC,ROLE,FT> (every launch of the sweep is an instance)",
+        "algorithmic_bytes_per_point": alg_bytes_point,
+        "dominant_point": dominant,
+        "per_point": per_point,
+    }
+    cpu = None
+    if not a.no_cpu:
+        gf, t, workers, ls, _ = cpu_sweep(a)
+        cpu = {"value": gf, "unit": "GFLOPS", "cores": workers, "kind": "port",
+               "sample": f"2^{ls} elements per sweep point (1/{1 << (a.log_total - ls)} of the batch), scipy.fft/pocketfft, "
+                         f"{t:.1f} s of CPU work"}
+    line = {
+        "metric": METRIC, "value": value, "unit": "GFLOPS", "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3),
+        "ms_per_step": t_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if a.datatype == 0 else "f64", "data": "synthetic",
+        "config": {"workload": workload_name(a), "thread_bs": a.thread_bs,
+                   "l2": f"inputs larger than L2 ({int(n * esize) >> 20} MiB per point vs {L2_BYTES >> 20} MiB)",
+                   "sharding": "batch sharded, each GPU its own 2^%d elements per point, no collective" % a.log_total},
+        "hbm_gbs_algorithmic": achieved,
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "check": {"parseval_rel_err_logN_%d" % logn_chk: parseval}, "ft": ft_info, "cufft": cufft,
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    a = parse_args()
+    if a.impl == "reference":
+        return run_reference(a)
+    return run_ours(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

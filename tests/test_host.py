@@ -1,0 +1,125 @@
+"""CPU tests of the host logic: parameter files, planner mirror, generator, C ABI surface."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+from turbofft_b200 import planner  # noqa: E402
+
+
+@pytest.mark.parametrize("dt", ["float2", "double2"])
+def test_b200_param_tables_are_valid(dt):
+    rows = planner.load_params(dt)
+    assert rows[0].launches == 0            # row 0 is the all-zero filler, as in the reference CSVs
+    for logn in range(1, 31):
+        r = rows[logn]
+        planner.validate_row(r)
+        ls = planner.launches_of_row(r)
+        assert len(ls) == r.launches
+        assert sum(l.logm for l in ls) == logn
+        for l in ls:
+            assert 1 <= l.threads <= 1024
+            if l.role == planner.ROLE_LAST:
+                assert l.stages >= 2 and l.logc <= l.log_n1
+            if l.role == planner.ROLE_FIRST:
+                assert l.logc <= l.log_b
+
+
+def test_reference_format_rows_parse():
+    # rows in the reference's own format (readme.md:48-60)
+    text = "14, 2, 7, 7, 0, 16, 16, 0, 8, 8, 0\n24, 3, 8, 8, 8, 16, 16, 16,  16, 16, 16\n"
+    rows = planner.parse_param_csv(text)
+    assert rows[14].logni[:2] == (7, 7) and rows[24].launches == 3
+    ls = planner.launches_of_row(rows[24])
+    assert [l.role for l in ls] == [planner.ROLE_FIRST, planner.ROLE_FIRST, planner.ROLE_LAST]
+    assert ls[0].log_b == 16 and ls[1].log_b == 8 and ls[2].log_n1 == 8 and ls[2].log_q == 8
+
+
+def test_bad_rows_rejected():
+    with pytest.raises(ValueError):
+        planner.parse_param_csv("1, 2, 3\n")
+    rows = planner.parse_param_csv("10, 1, 9, 0, 0, 1, 0, 0, 16, 0, 0\n")
+    with pytest.raises(ValueError):
+        planner.validate_row(rows[10])       # sizes do not add up
+    rows = planner.parse_param_csv("10, 1, 10, 0, 0, 3, 0, 0, 16, 0, 0\n")
+    with pytest.raises(ValueError):
+        planner.validate_row(rows[10])       # BS not a power of two
+
+
+def test_codegen_cli_flags(tmp_path):
+    """Same flags as the reference generator (fft_codegen.py:709-723)."""
+    gen = os.path.join(ROOT, "turbofft_b200", "codegen", "fft_codegen.py")
+    out = tmp_path / "gen"
+    for extra, mode in ([], 0), (["--if_ft", "1"], 1), (["--if_ft", "1", "--if_err_injection", "1"], 2):
+        subprocess.run([sys.executable, gen, "--datatype", "float2", "--gpu", "B200", "--err_inj", "7",
+                        "--err_smoothing", "500", "--err_threshold", "0.01", "--out", str(out)] + extra, check=True)
+        files = sorted(os.listdir(out / "float2"))
+        assert any(f.startswith(f"inst_ft{mode}_p") for f in files)
+    text = (out / "ft_defaults.h").read_text()
+    assert "TFFT_DEFAULT_ERR_INJ 7.0" in text and "TFFT_DEFAULT_ERR_SMOOTHING 500.0" in text
+    assert "TFFT_DEFAULT_ERR_THRESHOLD 0.01" in text
+    inst = (out / "float2" / "inst_ft2_p0.cu").read_text()
+    assert "TFFT_INST(float, 0," in inst
+    assert (out / "default_params_float2.inc").read_text().count("\\n") == 31
+
+
+def _declared_symbols():
+    hdr = open(os.path.join(ROOT, "include", "turbofft_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    return sorted(set(re.findall(r"\b(tfft_[a-z0-9_]+)\s*\(", hdr)))
+
+
+def test_library_exports_every_declared_symbol():
+    from turbofft_b200 import _lib
+
+    lib = _lib.lib()                      # raises if the .so was not built
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/turbofft_b200.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+
+
+def test_bad_arguments_fail_before_any_cuda_call():
+    from turbofft_b200 import _lib
+
+    lib = _lib.lib()
+    h = ctypes.c_void_p()
+    assert lib.tfft_plan_create(ctypes.byref(h), 0, 1, 0, 0, 0, 1, None, 0) == -1
+    assert lib.tfft_plan_create(ctypes.byref(h), 10, 0, 0, 0, 0, 1, None, 0) == -1
+    assert lib.tfft_plan_create(ctypes.byref(h), 10, 1, 7, 0, 0, 1, None, 0) == -1
+    assert lib.tfft_plan_create(None, 10, 1, 0, 0, 0, 1, None, 0) == -1
+    assert lib.tfft_plan_create(ctypes.byref(h), 10, 1, 0, 0, 0, 1, b"/nonexistent.csv", 0) == -4
+    assert lib.tfft_exec(None, None, None, None) == -1
+    assert lib.tfft_stream_copy(None, None, 16, None) == -1
+    assert lib.tfft_status_string(-2).startswith(b"unsupported")
+    assert lib.tfft_launch_count() == 0
+
+
+def test_no_cpu_fallback_without_gpu():
+    """Without a device the product path must fail loudly, not compute elsewhere."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    import turbofft_b200 as tf
+
+    with pytest.raises(tf.TurboFFTError):
+        tf.Plan(10, 16, 0)
+    with pytest.raises((ValueError, RuntimeError, tf.TurboFFTError)):
+        tf.fft(torch.zeros(4, 16, dtype=torch.complex64))
+
+
+def test_product_never_imports_oracle():
+    """The oracle is test infrastructure: nothing under turbofft_b200/ may use it."""
+    pkg = os.path.join(ROOT, "turbofft_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"(import\s+oracle|from\s+oracle|oracle/)", text), os.path.join(dirpath, f)

@@ -143,6 +143,8 @@ def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None):
     Power-of-two lengths 2..2^30; leading axes are the batch.  ft/err are the
     reference's --if_ft / --if_err.  Plans are cached per (device, shape, mode).
     """
+    if not x.is_cuda:
+        raise ValueError("turbofft_b200.fft needs a CUDA tensor: there is no CPU path")
     n = x.shape[-1]
     logn = n.bit_length() - 1
     if n < 2 or (1 << logn) != n:

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -22,6 +24,17 @@ using namespace tfft;
 namespace {
 
 std::atomic<long long> g_launches{0};
+
+// Device staging buffers of tfft_exec_host, one grow-only pair per device shared by all
+// plans (a sweep over many plans would otherwise hold one pair per plan).  Calls are
+// serialised by the mutex; each call synchronises before it returns.
+struct StagePair {
+    void* in = nullptr;
+    void* out = nullptr;
+    size_t bytes = 0;
+};
+std::mutex g_stage_mu;
+std::map<int, StagePair> g_stage;
 
 struct LaunchDesc {
     int role = 0, logm = 0, loge = 0, logc = 0;
@@ -68,8 +81,6 @@ struct tfft_plan_s {
     int diag = 0;
     cudaStream_t last_stream = nullptr;
     int last_cuda_error = 0;
-    void* stage_in = nullptr;
-    void* stage_out = nullptr;
     std::vector<void*> allocs;
     size_t esize() const { return dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2); }
 };
@@ -385,16 +396,24 @@ int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* strea
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
     const size_t bytes = ((size_t)p->batch << p->logn) * p->esize();
-    if (!p->stage_in) {
-        p->stage_in = dev_alloc(p, bytes);
-        p->stage_out = dev_alloc(p, bytes);
-        if (!p->stage_in || !p->stage_out) return TFFT_ERR_ALLOC;
+    std::lock_guard<std::mutex> lock(g_stage_mu);
+    StagePair& sp = g_stage[p->device];
+    if (sp.bytes < bytes) {
+        if (sp.in) cudaFree(sp.in);
+        if (sp.out) cudaFree(sp.out);
+        sp = StagePair();
+        if (!cuda_ok(p, cudaMalloc(&sp.in, bytes)) || !cuda_ok(p, cudaMalloc(&sp.out, bytes))) {
+            if (sp.in) cudaFree(sp.in);
+            sp = StagePair();
+            return TFFT_ERR_ALLOC;
+        }
+        sp.bytes = bytes;
     }
     cudaStream_t st = (cudaStream_t)stream;
-    if (!cuda_ok(p, cudaMemcpyAsync(p->stage_in, in_host, bytes, cudaMemcpyHostToDevice, st))) return TFFT_ERR_CUDA;
-    const int rc = tfft_exec(p, p->stage_in, p->stage_out, stream);
+    if (!cuda_ok(p, cudaMemcpyAsync(sp.in, in_host, bytes, cudaMemcpyHostToDevice, st))) return TFFT_ERR_CUDA;
+    const int rc = tfft_exec(p, sp.in, sp.out, stream);
     if (rc != TFFT_OK) return rc;
-    if (!cuda_ok(p, cudaMemcpyAsync(out_host, p->stage_out, bytes, cudaMemcpyDeviceToHost, st))) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaMemcpyAsync(out_host, sp.out, bytes, cudaMemcpyDeviceToHost, st))) return TFFT_ERR_CUDA;
     if (!cuda_ok(p, cudaStreamSynchronize(st))) return TFFT_ERR_CUDA;
     return TFFT_OK;
 }
