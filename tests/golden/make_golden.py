@@ -17,7 +17,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 from oracle import fft_oracle as orc  # noqa: E402
 
-CASES = [(0, 1, 64), (0, 4, 32), (0, 7, 16), (0, 10, 16), (0, 12, 4), (0, 14, 8), (0, 16, 8),
+# float2 logN 2..4 are refused by the harness (stale reference kernels, see oracle/ref_harness.cu)
+CASES = [(0, 1, 64), (0, 5, 32), (0, 7, 16), (0, 10, 16), (0, 12, 4), (0, 14, 8), (0, 16, 8),
          (1, 3, 32), (1, 10, 16), (1, 13, 4), (1, 15, 8)]
 
 
