@@ -117,8 +117,8 @@ void fill_twiddles(std::vector<C>& v, long long count, long long stride, int log
 
 // Stage twiddles of the in-block Stockham exchange, in the order the kernel reads them
 // (fft_kernels.cuh, KernelArgs::tw_st): for stage t with radix R_t = 2^lr and already
-// transformed extent P_t = 2^lp, entry (q, b) = W_M^{(b >> lp) * q << lp} for q = 1..R_t-1
-// and butterfly b < M / R_t.
+// transformed extent P_t = 2^lp, entry (j, b) = W_M^{((b >> lp) << lp) * 2^j} for j < lr and
+// butterfly b < M / R_t.
 template <typename C>
 void stage_twiddles(std::vector<C>& v, int logm, int loge) {
     v.clear();
@@ -129,7 +129,8 @@ void stage_twiddles(std::vector<C>& v, int logm, int loge) {
     for (int t = 0; t + 1 < stages; ++t) {
         const int lr = t == 0 ? logr0 : loge;
         const int lp = t == 0 ? 0 : logr0 + (t - 1) * loge;
-        for (long long q = 1; q < (1LL << lr); ++q) {
+        for (int j = 0; j < lr; ++j) {
+            const long long q = 1LL << j;
             for (long long b = 0; b < (m >> lr); ++b) {
                 const long long idx = (((b >> lp) * q) << lp) & (m - 1);
                 const long double ang = -two_pi * (long double)idx / (long double)m;

@@ -44,8 +44,8 @@ struct KernelArgs {
     const C* in;
     C* out;
     const C* tw_st;  // in-block stage twiddles, laid out so that a warp reads them coalesced:
-                     // stage t, output q >= 1, butterfly b -> W_M^{(b >> logP_t) * q << logP_t}
-                     // at stage_offset(t) + (q - 1) * (M / R_t) + b
+                     // stage t, j < log2 R_t, butterfly b -> w^(2^j) with w = W_M^{(b >> logP_t) << logP_t}
+                     // at stage_offset(t) + j * (M / R_t) + b; the other powers are products of these
     const C* tw_lo;  // W_P^j, j < 2^tw_lo_bits (inter-launch twiddle, low part)
     const C* tw_hi;  // W_P^(j << tw_lo_bits)   (high part), P = M * B
     const C* cks;    // c = W_M r, M entries    (FT only)
@@ -158,6 +158,24 @@ __device__ __forceinline__ void dif_butterfly(C (&v)[E], const int u) {
     if constexpr (LR > 0) dif_level<LR, LR - 1, STR, T>(v, u);
 }
 
+// ---------------------------------------------------------------- shared-memory layout
+// pad(a) = a + (a >> PADSHIFT); rows layout (ROLE_SINGLE, ROLE_LAST): line pitch =
+// pad(M - 1) + 1 + EXTRA; cols layout (ROLE_FIRST): position pad(a) * C + c.  The primary
+// template is a reasonable default; generated/smem_layouts.h specialises it per instance
+// with the conflict-free choice found by codegen/smem_layout.py.
+template <typename T, int LOGM, int LOGE, int LOGC, int ROLE>
+struct SmemLayout {
+    static constexpr int M = 1 << LOGM;
+    static constexpr int TPL = 1 << (LOGM - LOGE);
+    static constexpr int BANKW = 128 / (2 * (int)sizeof(T));
+    static constexpr int PADSHIFT = ROLE == ROLE_FIRST ? 31 : (sizeof(T) == 4 ? 4 : 3);
+    static constexpr int MPAD = (M - 1) + ((M - 1) >> PADSHIFT) + 1;
+    static constexpr int EXTRA = ROLE == ROLE_FIRST ? 0
+                                 : ROLE == ROLE_LAST ? ((MPAD | 1) - MPAD)
+                                 : (TPL >= BANKW ? 0 : ((MPAD + BANKW - 1) / BANKW) * BANKW + TPL - MPAD);
+};
+#include "generated/smem_layouts.h"
+
 // ---------------------------------------------------------------- configuration
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE>
 struct Cfg {
@@ -175,13 +193,11 @@ struct Cfg {
     static constexpr bool CFAST_IN = (ROLE == ROLE_FIRST);
     static constexpr bool CFAST_OUT = (ROLE != ROLE_SINGLE);
     static constexpr bool LAYOUT_COLS = (ROLE == ROLE_FIRST);
-    static constexpr int BANKW = 128 / (2 * (int)sizeof(T));  // complex elements per 128 B
-    static constexpr int PADSHIFT = sizeof(T) == 4 ? 4 : 3;
-    static constexpr int MPAD = M + (M >> PADSHIFT);
-    static constexpr int PITCH =
-        ROLE == ROLE_LAST ? (MPAD | 1)
-        : (TPL >= BANKW ? MPAD : ((MPAD + BANKW - 1) / BANKW) * BANKW + TPL);
-    static constexpr int SMEM_ELEMS = S > 1 ? (LAYOUT_COLS ? M * C : PITCH * C) : 0;
+    typedef SmemLayout<T, LOGM, LOGE, LOGC, ROLE> L;
+    static constexpr int PADSHIFT = L::PADSHIFT;
+    static constexpr int MPAD = (M - 1) + ((M - 1) >> PADSHIFT) + 1;
+    static constexpr int PITCH = MPAD + L::EXTRA;
+    static constexpr int SMEM_ELEMS = S > 1 ? (LAYOUT_COLS ? MPAD * C : PITCH * C) : 0;
     static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
     // Occupancy target handed to the compiler as the register cap: enough blocks for
     // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
@@ -212,12 +228,12 @@ struct Fft {
 
     template <int ST> static __device__ __forceinline__ constexpr int logR() { return ST == 0 ? K::LOGR0 : LOGE; }
     template <int ST> static __device__ __forceinline__ constexpr int logP() { return ST == 0 ? 0 : K::LOGR0 + (ST - 1) * LOGE; }
-    // first entry of stage ST in the stage-twiddle table: sum over earlier stages of (R - 1) * M / R
+    // first entry of stage ST in the stage-twiddle table: sum over earlier stages of log2(R) * M / R
     template <int ST> static __device__ __forceinline__ constexpr int twOff() {
         int off = 0;
         for (int t = 0; t < ST; ++t) {
             const int lr = t == 0 ? K::LOGR0 : LOGE;
-            off += ((1 << lr) - 1) << (LOGM - lr);
+            off += lr << (LOGM - lr);
         }
         return off;
     }
@@ -238,11 +254,11 @@ struct Fft {
     // occupy disjoint bit fields, which lets every unrolled access use a constant offset
     // from one per-thread base.
     static __device__ __forceinline__ int soff(int a, int c) {
-        if (K::LAYOUT_COLS) return a * K::C + c;
+        if (K::LAYOUT_COLS) return (a + (a >> K::PADSHIFT)) * K::C + c;
         return c * K::PITCH + a + (a >> K::PADSHIFT);
     }
     static __device__ __forceinline__ constexpr int sdelta(int y) {
-        return K::LAYOUT_COLS ? y * K::C : y + (y >> K::PADSHIFT);
+        return K::LAYOUT_COLS ? (y + (y >> K::PADSHIFT)) * K::C : y + (y >> K::PADSHIFT);
     }
 
     static __device__ __forceinline__ Geom decode(const KernelArgs<T>& a, long long tile) {
@@ -351,11 +367,20 @@ struct Fft {
                 const int nlo = b >> LP;
                 // p, q << LP and nlo << (LP + LR) are disjoint bit fields of the address
                 C* wr = sm + soff(p + (nlo << (LP + LR)), c);
+                // w^q for q < R: the log2(R) powers w^(2^j) come from the table, every other
+                // power is one product of two already known ones (at most log2(R) table
+                // entries deep, so the rounding of a table entry is never amplified)
                 const C* tw = a.tw_st + twOff<ST>() + b;
+                C w[R];
+#pragma unroll
+                for (int j = 0; j < LR; ++j) w[1 << j] = __ldg(tw + j * (K::M / R));
+#pragma unroll
+                for (int q = 3; q < R; ++q)
+                    if (q & (q - 1)) w[q] = cmul(w[q - (1 << ilog2(q))], w[1 << ilog2(q)]);
 #pragma unroll
                 for (int q = 0; q < R; ++q) {
                     C val = v[u + brev<LR>(q) * NB];
-                    if (q > 0) val = cmul(val, __ldg(tw + (q - 1) * (K::M / R)));
+                    if (q > 0) val = cmul(val, w[q]);
                     wr[sdelta(q << LP)] = val;
                 }
             }
