@@ -120,11 +120,15 @@ long long tfft_launch_count(void);
 int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream);
 
 /* Building blocks of the multi-GPU four-step transform (no counterpart in the
- * reference, which is single-GPU).  Both work on a local [rows][cols] complex
- * matrix in device memory.
- * tfft_transpose:         dst[c][r] = src[r][c]
+ * reference, which is single-GPU).  They work on local complex arrays in device
+ * memory.
+ * tfft_transpose:         [rows][cols] -> dst[c][r] = src[r][c]
  * tfft_twiddle_transpose: dst[c][r] = src[r][c] * exp(-2*pi*i * (row0 + r) * (col0 + c) / 2^log_total)
+ * tfft_permute102:        [A][B][run] -> dst[b][a][:] = src[a][b][:]  (pack / unpack of the
+ *                         all-to-all exchanges; run * sizeof(element) must be a multiple of 16)
  */
+int tfft_permute102(const void* src, void* dst, long long A, long long B, long long run_elems, int dtype,
+                    void* stream);
 int tfft_transpose(const void* src, void* dst, long long rows, long long cols, int dtype, void* stream);
 int tfft_twiddle_transpose(const void* src, void* dst, long long rows, long long cols, long long row0,
                            long long col0, int log_total, int dtype, void* stream);

@@ -1,0 +1,193 @@
+"""Multi-GPU layer: distribution logic on CPU ranks (gloo), kernels on one GPU, and a
+2-GPU run where the machine has two."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from oracle import fft_oracle as orc  # noqa: E402
+from turbofft_b200 import multi_gpu as mg  # noqa: E402
+
+
+def test_shard_range_covers_everything():
+    for total, world in [(16, 4), (17, 4), (3, 8), (1 << 20, 8)]:
+        spans = [mg.shard_range(total, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
+    assert mg.split_log(30) == (15, 15) and mg.split_log(29) == (15, 14)
+
+
+class HostBackend:
+    """CPU stand-in for the device operations (numpy + the oracle FFT), used only to check
+    the index logic and the all-to-all plumbing of FourStepFFT between gloo ranks."""
+
+    def __init__(self, torch):
+        self.torch = torch
+
+    def _np(self, x):
+        return x.numpy()
+
+    def fft_rows(self, x, logn):
+        y = orc.fft_forward(self._np(x).reshape(-1, 1 << logn))
+        return self.torch.from_numpy(np.ascontiguousarray(y.reshape(-1)))
+
+    def transpose(self, x, rows, cols):
+        return self.torch.from_numpy(np.ascontiguousarray(self._np(x).reshape(rows, cols).T).reshape(-1))
+
+    def twiddle_transpose(self, x, rows, cols, row0, col0, log_total):
+        r = np.arange(rows)[:, None] + row0
+        c = np.arange(cols)[None, :] + col0
+        n = 1 << log_total
+        w = np.exp(-2j * np.pi * ((r * c) % n) / n)
+        return self.torch.from_numpy(np.ascontiguousarray((self._np(x).reshape(rows, cols) * w).T).reshape(-1))
+
+    def permute102(self, x, a, b, run):
+        return self.torch.from_numpy(np.ascontiguousarray(self._np(x).reshape(a, b, run).transpose(1, 0, 2)).reshape(-1))
+
+    def all_to_all(self, x, group):
+        import torch.distributed as dist
+
+        out = self.torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=group)
+        return out
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _cpu_worker(rank, world, port, logn, natural, q):
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = 1 << logn
+        x = orc.make_input(1, n, np.complex128, seed=42)[0]
+        b, e = mg.shard_range(n, world, rank)
+        fs = mg.FourStepFFT(logn, world, rank, HostBackend(torch), natural_order=natural)
+        y = fs(torch.from_numpy(x[b:e].copy())).numpy()
+        ref = orc.fft_forward(x)
+        if natural:
+            err = orc.rel_l2(y, ref[b:e])
+        else:
+            n1l = fs.n1 // world
+            idx = np.array([[fs.output_index(k1, k2) for k2 in range(fs.n2)] for k1 in range(n1l)]).reshape(-1)
+            err = orc.rel_l2(y, ref[idx])
+        q.put((rank, err))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,logn,natural", [(2, 10, False), (2, 11, True), (4, 12, False), (4, 13, True)])
+def test_four_step_distribution_logic_gloo(world, logn, natural):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_worker, args=(r, world, port, logn, natural, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    res = dict(q.get(timeout=10) for _ in range(world))
+    assert len(res) == world and all(e < 1e-12 for e in res.values()), res
+
+
+def test_batch_sharding_is_communication_free_gloo():
+    """Each rank transforms its own contiguous batch range; concatenation equals the whole."""
+    x = orc.make_input(10, 64, np.complex128, seed=3)
+    parts = []
+    for r in range(4):
+        b, e = mg.shard_range(10, 4, r)
+        parts.append(orc.fft_forward(x[b:e]))
+    assert orc.rel_l2(np.concatenate(parts), orc.fft_forward(x)) == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,logn,natural", [(0, 16, False), (0, 17, True), (1, 14, True), (1, 20, False)])
+def test_four_step_kernels_single_gpu(torch_cuda, dtype, logn, natural):
+    """World size 1: no exchange, but every local kernel of the four-step path runs."""
+    torch = torch_cuda
+    npdt = np.complex64 if dtype == 0 else np.complex128
+    x = orc.make_input(1, 1 << logn, npdt, seed=logn)[0]
+    fs = mg.FourStepFFT(logn, 1, 0, mg.DeviceBackend(dtype, 0), natural_order=natural)
+    y = fs(torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = orc.fft_forward(x)
+    if not natural:
+        ref = ref.reshape(fs.n2, fs.n1).T.reshape(-1)   # [k1][k2]
+    assert orc.rel_l2(y, ref) <= orc.tolerance(npdt, logn)
+
+
+@pytest.mark.gpu
+def test_helper_kernels(torch_cuda):
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    be = mg.DeviceBackend(1, 0)
+    x = torch.randn(6 * 10 * 4, dtype=torch.complex128, device="cuda")
+    assert torch.equal(be.permute102(x, 6, 10, 4).view(10, 6, 4), x.view(6, 10, 4).permute(1, 0, 2))
+    assert torch.equal(be.transpose(x, 24, 10).view(10, 24), x.view(24, 10).t())
+    t = be.twiddle_transpose(x, 24, 10, 5, 3, 12).view(10, 24).cpu().numpy()
+    r = np.arange(24)[:, None] + 5
+    c = np.arange(10)[None, :] + 3
+    w = np.exp(-2j * np.pi * ((r * c) % 4096) / 4096)
+    assert np.allclose(t, (x.view(24, 10).cpu().numpy() * w).T, atol=1e-13)
+    src = torch.arange(1 << 20, dtype=torch.float32, device="cuda")
+    dst = torch.zeros_like(src)
+    tf.stream_copy(src, dst)
+    assert torch.equal(src, dst)
+
+
+def _gpu_worker(rank, world, port, logn, dtype, q):
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        npdt = np.complex64 if dtype == 0 else np.complex128
+        n = 1 << logn
+        x = orc.make_input(1, n, npdt, seed=7)[0]
+        b, e = mg.shard_range(n, world, rank)
+        fs = mg.FourStepFFT(logn, world, rank, mg.DeviceBackend(dtype, rank, if_ft=1), natural_order=True)
+        y = fs(torch.from_numpy(x[b:e].copy()).cuda()).cpu().numpy()
+        q.put((rank, orc.rel_l2(y, orc.fft_forward(x)[b:e])))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,logn", [(0, 20), (1, 19)])
+def test_four_step_two_gpus(torch_cuda, dtype, logn):
+    torch = torch_cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_worker, args=(r, 2, port, logn, dtype, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    res = dict(q.get(timeout=10) for _ in range(2))
+    tol = orc.tolerance(np.complex64 if dtype == 0 else np.complex128, logn)
+    assert all(e <= tol for e in res.values()), res

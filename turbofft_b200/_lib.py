@@ -37,6 +37,7 @@ SIGNATURES = {
     "tfft_launch_count": (C.c_longlong, []),
     "tfft_stream_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tfft_transpose": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p]),
+    "tfft_permute102": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p]),
     "tfft_twiddle_transpose": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_longlong, C.c_longlong,
                                          C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
 }

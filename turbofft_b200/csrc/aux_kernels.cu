@@ -62,6 +62,20 @@ __global__ void __launch_bounds__(256) transpose_kernel(const C* __restrict__ sr
     }
 }
 
+// dst[b][a][0..run) = src[a][b][0..run): swaps the two outer axes of an [A][B][run] array
+// whose innermost runs are contiguous; run is counted in 16-byte words.
+__global__ void __launch_bounds__(256) permute102_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                                         long long A, long long B, long long run) {
+    const long long total = A * B * run;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long w = i % run;
+        const long long ab = i / run;
+        const long long a = ab % A, b = ab / A;  // i enumerates the destination [b][a][w]
+        dst[i] = __ldcs(src + (a * B + b) * run + w);
+    }
+}
+
 template <bool TW>
 int launch_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
                      int log_total, int dtype, void* stream) {
@@ -91,6 +105,21 @@ int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream) {
     const size_t blocks = (n + 511) / 512;
     if (blocks > 2147483647ULL) return TFFT_ERR_TOO_LARGE;
     stream_copy_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, n);
+    tfft::note_launch();
+    return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+int tfft_permute102(const void* src, void* dst, long long A, long long B, long long run_elems, int dtype,
+                    void* stream) {
+    if (!src || !dst || A < 1 || B < 1 || run_elems < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
+        return TFFT_ERR_BAD_ARG;
+    const long long bytes = run_elems * (dtype == TFFT_FLOAT2 ? 8 : 16);
+    if ((bytes & 15) || (((size_t)src | (size_t)dst) & 15)) return TFFT_ERR_BAD_ARG;
+    const long long run = bytes / 16;
+    const long long total = A * B * run;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 64) blocks = 148LL * 64;
+    permute102_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, A, B, run);
     tfft::note_launch();
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
 }

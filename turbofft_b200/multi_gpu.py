@@ -1,0 +1,153 @@
+"""Multi-GPU layer: one process per GPU, torch.distributed (NCCL over NVLink) for the plumbing.
+
+The reference is single-GPU (no NCCL/MPI anywhere; its device/default_fft.h:14 only has a
+"support multi nodes" to-do), so this layer has no reference counterpart; it is built from
+the single-GPU plan (the C ABI) plus three helper kernels.
+
+* Batched transforms shard by batch: `shard_range` gives each rank a contiguous range of
+  signals and the rank runs an ordinary Plan on it.  No communication.
+* One transform too large for a GPU uses the four-step decomposition over N = N1 * N2 seen
+  as an N1 x N2 row-major matrix whose rows are block-distributed:
+    1. all-to-all so that each rank holds N2/P columns with all N1 rows, transposed locally
+       to [N2/P][N1]
+    2. N2/P local FFTs of length N1 (a Plan, FT on if asked), then a transpose fused with the
+       twiddle W_N^(n2*k1) giving [N1][N2/P]
+    3. all-to-all back: each rank holds N1/P values of k1 with all n2, [N1/P][N2]
+    4. N1/P local FFTs of length N2
+  The result is X[k1 + N1*k2] at rank(k1), position [k1_local][k2] ("transposed out", what
+  FFTW-MPI and cuFFTMp call it); natural_order=True adds a third exchange that leaves each
+  rank with its contiguous slab of X.
+The all-to-all is torch.distributed.all_to_all_single; every kernel touches local memory
+only (remote data always lands in local HBM first).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Tuple
+
+from . import _lib
+from ._lib import lib
+
+
+def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [begin, end) of `total` items for `rank`; sizes differ by at most one."""
+    base, rem = divmod(total, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+def split_log(logn: int) -> Tuple[int, int]:
+    """(log2 N1, log2 N2) with N1 >= N2: 2^30 -> 2^15 x 2^15, 2^29 -> 2^15 x 2^14."""
+    l1 = (logn + 1) // 2
+    return l1, logn - l1
+
+
+class DeviceBackend:
+    """Local operations of the four-step transform on CUDA tensors, through the C ABI."""
+
+    def __init__(self, dtype_code: int, device_index: int, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1):
+        import torch
+
+        from . import Plan
+
+        self.torch = torch
+        self.Plan = Plan
+        self.dt = dtype_code
+        self.dev = device_index
+        self.if_ft, self.if_err, self.thread_bs = if_ft, if_err, thread_bs
+        self.plans = {}
+
+    def _stream(self):
+        return self.torch.cuda.current_stream(self.dev).cuda_stream
+
+    def empty_like(self, x):
+        return self.torch.empty_like(x)
+
+    def fft_rows(self, x, logn: int):
+        """FFT of every contiguous length-2^logn row of x (any leading shape)."""
+        batch = x.numel() >> logn
+        key = (logn, batch)
+        if key not in self.plans:
+            self.plans[key] = self.Plan(logn, batch, self.dt, self.if_ft, self.if_err, self.thread_bs, device=self.dev)
+        out = self.torch.empty_like(x)
+        self.plans[key].exec_ptr(x.data_ptr(), out.data_ptr(), self._stream())
+        return out
+
+    def transpose(self, x, rows: int, cols: int):
+        out = self.torch.empty_like(x)
+        _lib.check(lib().tfft_transpose(x.data_ptr(), out.data_ptr(), rows, cols, self.dt, self._stream()), "tfft_transpose")
+        return out
+
+    def twiddle_transpose(self, x, rows: int, cols: int, row0: int, col0: int, log_total: int):
+        out = self.torch.empty_like(x)
+        _lib.check(lib().tfft_twiddle_transpose(x.data_ptr(), out.data_ptr(), rows, cols, row0, col0, log_total, self.dt,
+                                                self._stream()), "tfft_twiddle_transpose")
+        return out
+
+    def permute102(self, x, a: int, b: int, run: int):
+        out = self.torch.empty_like(x)
+        _lib.check(lib().tfft_permute102(x.data_ptr(), out.data_ptr(), a, b, run, self.dt, self._stream()), "tfft_permute102")
+        return out
+
+    def all_to_all(self, x, group):
+        import torch.distributed as dist
+
+        out = self.torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=group)
+        return out
+
+    def ft_counts(self):
+        """(blocks that detected, tiles recomputed) summed over the local plans' last runs."""
+        nd = nc = 0
+        for p in self.plans.values():
+            d, c, _ = p.ft_status()
+            nd += d
+            nc += c
+        return nd, nc
+
+
+class FourStepFFT:
+    """Distributed 1-D FFT of length 2^logn over the ranks of `group`.
+
+    Input: this rank's rows of the N1 x N2 matrix, i.e. elements
+    [rank*N/P, (rank+1)*N/P) of the signal.  Output: see module docstring.
+    `backend` supplies the local operations (DeviceBackend on GPUs; tests inject a host
+    stand-in to check the distribution logic with gloo).
+    """
+
+    def __init__(self, logn: int, world: int, rank: int, backend, group=None, natural_order: bool = False):
+        self.logn, self.world, self.rank = logn, world, rank
+        self.l1, self.l2 = split_log(logn)
+        self.n1, self.n2 = 1 << self.l1, 1 << self.l2
+        if self.n1 % world or self.n2 % world:
+            raise ValueError("world size must divide both factors of the transform")
+        self.be, self.group, self.natural = backend, group, natural_order
+
+    def __call__(self, x_local):
+        be, P, r = self.be, self.world, self.rank
+        n1, n2, n1l, n2l = self.n1, self.n2, self.n1 // P, self.n2 // P
+        # 1. [n1l][P][n2l] -> [P][n1l][n2l], exchange, recv = [N1][n2l], transpose -> [n2l][N1]
+        a = be.permute102(x_local, n1l, P, n2l)
+        a = self._exchange(a)
+        a = be.transpose(a, n1, n2l)
+        # 2. FFT over n1, then twiddle W_N^(n2*k1) fused with the transpose -> [N1][n2l]
+        a = be.fft_rows(a, self.l1)
+        a = be.twiddle_transpose(a, n2l, n1, r * n2l, 0, self.logn)
+        # 3. rows k1 of rank j are contiguous: exchange, recv = [P][n1l][n2l] -> [n1l][P][n2l] = [n1l][N2]
+        a = self._exchange(a)
+        a = be.permute102(a, P, n1l, n2l)
+        # 4. FFT over n2 -> Z[k1_local][k2]
+        a = be.fft_rows(a, self.l2)
+        if not self.natural:
+            return a
+        # natural order: X[k1 + N1*k2]; rank j gets k2 in its range: pack, exchange, transpose
+        a = be.permute102(a, n1l, P, n2l)
+        a = self._exchange(a)
+        return be.transpose(a, n1, n2l)      # [k2_local][k1] = this rank's slab of X
+
+    def _exchange(self, a):
+        return a if self.world == 1 else self.be.all_to_all(a, self.group)
+
+    def output_index(self, k1_local: int, k2: int) -> int:
+        """Global frequency index of element [k1_local][k2] of the transposed-out result."""
+        return (self.rank * (self.n1 // self.world) + k1_local) + self.n1 * k2
