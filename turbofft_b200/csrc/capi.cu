@@ -207,8 +207,9 @@ bool build_tables(tfft_plan p) {
                 checksum_vector(d.logm, re, im);
                 std::vector<C> c(re.size());
                 for (size_t k = 0; k < re.size(); ++k) {
-                    c[k].x = (T)re[k];
-                    c[k].y = (T)im[k];
+                    // stored as the two fold weights: fold(x * c) = x.x * (c.x + c.y) + x.y * (c.x - c.y)
+                    c[k].x = (T)(re[k] + im[k]);
+                    c[k].y = (T)(re[k] - im[k]);
                 }
                 if (!upload(p, c, &d.cks)) return false;
             }
@@ -350,7 +351,7 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
             break;
         }
         d.grid = (unsigned)grid;
-        if (d.k->smem > 48 * 1024) {
+        if (d.k->smem > 40 * 1024) {  // FT kernels add a little static shared memory on top
             if (!cuda_ok(p, cudaFuncSetAttribute(d.k->fn[ftmode], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)d.k->smem)))
                 status = TFFT_ERR_CUDA;

@@ -48,7 +48,7 @@ struct KernelArgs {
                      // at stage_offset(t) + j * (M / R_t) + b; the other powers are products of these
     const C* tw_lo;  // W_P^j, j < 2^tw_lo_bits (inter-launch twiddle, low part)
     const C* tw_hi;  // W_P^(j << tw_lo_bits)   (high part), P = M * B
-    const C* cks;    // c = W_M r, M entries    (FT only)
+    const C* cks;    // FT only, M entries: fold weights of c = W_M r as (c.x + c.y, c.x - c.y)
     long long n_tiles;
     long long n_lines;  // ROLE_SINGLE: number of signals (ragged last tile)
     int tiles_per_cta;  // the reference's thread_bs
@@ -201,11 +201,14 @@ struct Cfg {
     static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
     // Occupancy target handed to the compiler as the register cap: enough blocks for
     // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
+    // The FT variants carry the checksum state on top and get a quarter more registers.
     static constexpr int SMEM_BLOCKS = SMEM_BYTES ? (int)((220 * 1024) / SMEM_BYTES) : 32;
-    static constexpr int THREAD_BLOCKS = (sizeof(T) == 4 ? 1024 : 512) / THREADS;
-    static constexpr int MIN_BLOCKS =
-        (SMEM_BLOCKS < THREAD_BLOCKS ? SMEM_BLOCKS : THREAD_BLOCKS) < 1 ? 1
-        : (SMEM_BLOCKS < THREAD_BLOCKS ? SMEM_BLOCKS : THREAD_BLOCKS);
+    static constexpr int min_blocks(bool ft) {
+        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? 3 : 4) / 4;
+        const int tb = (target + THREADS - 1) / THREADS;
+        const int b = SMEM_BLOCKS < tb ? SMEM_BLOCKS : tb;
+        return b < 1 ? 1 : b;
+    }
 };
 
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
@@ -220,9 +223,10 @@ struct Fft {
         int ncols;
     };
 
-    // per-thread FT state that lives across the tiles of a block
+    // per-thread FT state that lives across the tiles of a block.  The left-checksum
+    // weights are NOT kept here: 2E registers per thread cost more (spills or occupancy)
+    // than re-reading them per tile from the L1-resident table.
     struct FtRegs {
-        T ca[E], cb[E];  // fold weights of the left checksum: c.x + c.y, c.x - c.y
         T al[3], be[3];  // fold weights of the right checksum, rotated by s mod 3
     };
 
@@ -318,21 +322,35 @@ struct Fft {
             }
         }
         if (ROLE == ROLE_FIRST) {
-            // y_k *= W_P^{col*k}, k = s + i*TPL: base * step^i with a log-depth power tree
+            // y_k *= W_P^{col*k}, k = s + i*TPL, i.e. base * step^i
             const unsigned long long col = (unsigned long long)(g.col0 + c);
             const unsigned long long pmask = (1ULL << (LOGM + a.log_b)) - 1;
             const unsigned long long lomask = (1ULL << a.tw_lo_bits) - 1;
             const unsigned long long jb = (col * (unsigned long long)s) & pmask;
             const unsigned long long js = (col * (unsigned long long)TPL) & pmask;
-            C w[E], pw[LOGE];
-            w[0] = cmul(__ldg(a.tw_lo + (jb & lomask)), __ldg(a.tw_hi + (jb >> a.tw_lo_bits)));
-            pw[0] = cmul(__ldg(a.tw_lo + (js & lomask)), __ldg(a.tw_hi + (js >> a.tw_lo_bits)));
+            // w_i = base * step^i is formed as A[i >> LL] * B[i & (2^LL - 1)] with
+            // A[a] = base * step^(a << LL), B[b] = step^b: about sqrt(E) live values instead of E,
+            // every w_i at most ~log2(E)+1 products deep.
+            constexpr int LL = LOGE / 2, LH = LOGE - LL, NLO = 1 << LL, NHI = 1 << LH;
+            C A[NHI], B[NLO];
+            A[0] = cmul(__ldg(a.tw_lo + (jb & lomask)), __ldg(a.tw_hi + (jb >> a.tw_lo_bits)));
+            B[0].x = T(1);
+            B[0].y = T(0);
+            const C step = cmul(__ldg(a.tw_lo + (js & lomask)), __ldg(a.tw_hi + (js >> a.tw_lo_bits)));
+            C big = step;  // becomes step^(2^LL)
+            if constexpr (NLO > 1) {
+                B[1] = step;
 #pragma unroll
-            for (int l = 1; l < LOGE; ++l) pw[l] = cmul(pw[l - 1], pw[l - 1]);
+                for (int b = 2; b < NLO; ++b) B[b] = (b & 1) ? cmul(B[b - 1], B[1]) : cmul(B[b / 2], B[b / 2]);
+                big = cmul(B[NLO / 2], B[NLO / 2]);
+            }
 #pragma unroll
-            for (int i = 1; i < E; ++i) w[i] = cmul(w[i - (1 << ilog2(i))], pw[ilog2(i)]);
+            for (int h = 1; h < NHI; ++h) A[h] = cmul(A[h - 1], big);
 #pragma unroll
-            for (int i = 0; i < E; ++i) y[i] = cmul(y[i], w[i]);
+            for (int i = 0; i < E; ++i) {
+                const C w = (i & (NLO - 1)) ? cmul(A[i >> LL], B[i & (NLO - 1)]) : A[i >> LL];
+                y[i] = cmul(y[i], w);
+            }
         }
         if (c < g.ncols) {
             C* dst = a.out + g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
@@ -409,10 +427,13 @@ struct Fft {
             for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
         }
         if (DO_FT) {
+            // fold(x * c) = x.x * (c.x + c.y) + x.y * (c.x - c.y); rows s + i*TPL, coalesced over s
+            const C* wt = a.cks + s;
 #pragma unroll
             for (int i = 0; i < E; ++i) {
-                tin = fma(v[i].x, f.ca[i], tin);
-                tin = fma(v[i].y, f.cb[i], tin);
+                const C w = __ldg(wt + i * TPL);
+                tin = fma(v[i].x, w.x, tin);
+                tin = fma(v[i].y, w.y, tin);
             }
         }
         if (DO_INJ) {
@@ -443,13 +464,6 @@ struct Fft {
         FtRegs f;
         {
             int s, c;
-            map_thread<K::CFAST_IN>(s, c);
-#pragma unroll
-            for (int i = 0; i < E; ++i) {
-                const C cc = __ldg(a.cks + s + i * TPL);
-                f.ca[i] = cc.x + cc.y;
-                f.cb[i] = cc.x - cc.y;
-            }
             map_thread<K::CFAST_OUT>(s, c);
             // r_j = omega^j with the float32-rounded imaginary part of the reference
             // (include/turbofft/constants.h:2-7)
@@ -526,7 +540,8 @@ struct Fft {
 };
 
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
-__global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS), (Cfg<T, LOGM, LOGE, LOGC, ROLE>::MIN_BLOCKS))
+__global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS),
+                                  (Cfg<T, LOGM, LOGE, LOGC, ROLE>::min_blocks(FT != FT_OFF)))
 fft_kernel(const __grid_constant__ KernelArgs<T> a) {
     extern __shared__ __align__(16) unsigned char tfft_smem_raw[];
     typedef typename Cplx<T>::type C;
