@@ -1,0 +1,197 @@
+"""Tuner for param/<gpu>/param_<datatype>.csv (the reference's 11-column format, readme.md:46-67).
+
+The reference ships hand-tuned A100/T4 tables; this searches the same space on the machine
+it runs on: launch split (logN1..3), lines per block (BSi) and points per thread (ni).
+
+  1. python -m turbofft_b200.tune emit --datatype float2          # CPU: candidate rows ->
+        param/B200/extra_float2.csv, then `python -m turbofft_b200.build` compiles them
+  2. python -m turbofft_b200.tune run --datatype float2 --out r.json   # GPU: times every candidate
+        at logN + logBS = --log-total (default 28), FT off
+  3. python -m turbofft_b200.tune apply --datatype float2 --results r.json   # CPU: best rows -> CSV
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import tempfile
+
+from . import planner
+
+MAX_SMEM = 110 * 1024
+
+
+def _row(logn, parts):
+    """parts: list of (logm, bs, n) per launch."""
+    l = len(parts)
+    logs = [p[0] for p in parts] + [0] * (3 - l)
+    bs = [p[1] for p in parts] + [0] * (3 - l)
+    n = [p[2] for p in parts] + [0] * (3 - l)
+    return planner.ParamRow(logn, l, tuple(logs), tuple(bs), tuple(n))
+
+
+def _launch_ok(logm, c, e, role, esize, n_first=None):
+    if e > (1 << logm):
+        return False
+    threads = ((1 << logm) // e) * c
+    if not 32 <= threads <= 1024:
+        return False
+    stages = (logm + (e.bit_length() - 1) - 1) // (e.bit_length() - 1)
+    if role == planner.ROLE_LAST and stages < 2:
+        return False
+    smem = (1 << logm) * c * esize * 1.3 if stages > 1 else 0
+    return smem <= MAX_SMEM
+
+
+def candidates(logn: int, datatype: str):
+    esize = 8 if datatype == "float2" else 16
+    es = (8, 16) if datatype == "double2" else (8, 16, 32)
+    out = []
+    if logn <= 14:
+        for e in es:
+            for c in (1, 2, 4, 8, 16, 32, 64, 128):
+                if _launch_ok(logn, c, min(e, 1 << logn), planner.ROLE_SINGLE, esize):
+                    out.append(_row(logn, [(logn, c, min(e, 1 << logn))]))
+    if logn >= 12:
+        for a in range(6, 13):
+            b = logn - a
+            if not 6 <= b <= 12 or abs(a - b) > 3:
+                continue
+            for e1 in (8, 16):
+                for e2 in (8, 16):
+                    for c1 in (4, 8, 16, 32):
+                        for c2 in (4, 8, 16, 32):
+                            if c2 > (1 << a):
+                                continue
+                            if _launch_ok(a, c1, e1, planner.ROLE_FIRST, esize) and _launch_ok(b, c2, e2, planner.ROLE_LAST, esize):
+                                out.append(_row(logn, [(a, c1, e1), (b, c2, e2)]))
+    if logn >= 20:
+        base = logn // 3
+        for a in range(base - 1, base + 3):
+            for b in range(base - 1, base + 3):
+                c = logn - a - b
+                if not 6 <= c <= 10 or not 6 <= a <= 10 or not 6 <= b <= 10:
+                    continue
+                for e in (8, 16):
+                    for cc in (8, 16, 32):
+                        if all(_launch_ok(m, cc, e, r, esize) for m, r in
+                               ((a, planner.ROLE_FIRST), (b, planner.ROLE_FIRST), (c, planner.ROLE_LAST))):
+                            out.append(_row(logn, [(a, cc, e), (b, cc, e), (c, cc, e)]))
+    # de-duplicate
+    seen, uniq = set(), []
+    for r in out:
+        key = (r.launches, r.logni, r.bs, r.n)
+        if key not in seen:
+            seen.add(key)
+            uniq.append(r)
+    return uniq
+
+
+def row_text(r: planner.ParamRow) -> str:
+    return ", ".join(str(v) for v in (r.logn, r.launches) + tuple(r.logni) + tuple(r.bs) + tuple(r.n))
+
+
+def cmd_emit(a):
+    path = os.path.join(planner.PARAM_DIR, a.gpu, f"extra_{a.datatype}.csv")
+    lines = ["# candidate rows for the tuner (python -m turbofft_b200.tune); compiled for FT off only"]
+    n = 0
+    for logn in range(a.lo, a.hi + 1):
+        for r in candidates(logn, a.datatype):
+            lines.append(row_text(r))
+            n += 1
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    print(f"wrote {n} candidate rows to {path}")
+
+
+def cmd_run(a):
+    import torch
+
+    import turbofft_b200 as tf
+
+    dt = 0 if a.datatype == "float2" else 1
+    td = torch.complex64 if dt == 0 else torch.complex128
+    n = 1 << a.log_total
+    x = torch.randn(n, dtype=td, device="cuda")
+    y = torch.empty_like(x)
+    stream = torch.cuda.current_stream().cuda_stream
+    current = planner.load_params(a.datatype, a.gpu)
+    results = {}
+    for logn in range(a.lo, a.hi + 1):
+        cands = [current[logn]] + candidates(logn, a.datatype)
+        best = None
+        rows = []
+        for r in cands:
+            with tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False) as f:
+                f.write(row_text(r) + "\n")
+                path = f.name
+            try:
+                plan = tf.Plan(logn, 1 << (a.log_total - logn), dt, param_csv=path)
+            except tf.TurboFFTError:
+                os.unlink(path)
+                continue
+            os.unlink(path)
+            for _ in range(2):
+                plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(a.reps):
+                plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / a.reps
+            plan.destroy()
+            rows.append((ms, row_text(r)))
+            if best is None or ms < best[0]:
+                best = (ms, row_text(r))
+        rows.sort()
+        results[str(logn)] = {"best": best, "current_ms": rows and next((m for m, t in rows if t == row_text(current[logn])), None),
+                              "top": rows[:5], "tried": len(rows)}
+        print(f"logN {logn}: best {best[0]:.3f} ms [{best[1]}] current {results[str(logn)]['current_ms']} ({len(rows)} tried)",
+              flush=True)
+    with open(a.out, "w") as f:
+        json.dump(results, f, indent=1)
+
+
+def cmd_apply(a):
+    res = json.load(open(a.results))
+    path = os.path.join(planner.PARAM_DIR, a.gpu, f"param_{a.datatype}.csv")
+    rows = planner.load_params(a.datatype, a.gpu)
+    lines = []
+    for logn in sorted(rows):
+        r = rows[logn]
+        key = str(logn)
+        if key in res and res[key]["best"] and (res[key]["current_ms"] is None or
+                                               res[key]["best"][0] < res[key]["current_ms"] * (1 - a.min_gain)):
+            lines.append(res[key]["best"][1])
+        else:
+            lines.append(row_text(r))
+    with open(path, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    print(f"updated {path}")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("emit", "run", "apply"):
+        p = sub.add_parser(name)
+        p.add_argument("--datatype", default="float2", choices=["float2", "double2"])
+        p.add_argument("--gpu", default="B200")
+        p.add_argument("--lo", type=int, default=7)
+        p.add_argument("--hi", type=int, default=24)
+        if name == "run":
+            p.add_argument("--log-total", type=int, default=28)
+            p.add_argument("--reps", type=int, default=5)
+            p.add_argument("--out", default="tune_results.json")
+        if name == "apply":
+            p.add_argument("--results", required=True)
+            p.add_argument("--min-gain", type=float, default=0.01)
+    a = ap.parse_args(argv)
+    {"emit": cmd_emit, "run": cmd_run, "apply": cmd_apply}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
