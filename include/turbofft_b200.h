@@ -107,6 +107,20 @@ int tfft_ft_diag(tfft_plan plan, int launch, double* diag, int cap_blocks);
 
 int tfft_plan_destroy(tfft_plan plan);
 
+/* No counterpart in the reference.  One-shot transform for callers that cannot allocate
+ * device memory when they call (no cudaMalloc allowed: pool-managed regions, allocation-free
+ * service loops, devices whose memory is fully handed out).  Runs the built-in multi-launch
+ * plan for (logN, dtype), FT off, with the intermediate buffer and the twiddle tables in
+ * static device arrays of the library (16 MiB + 512 KiB held by every GPU that loads it).
+ * Limits: the size must be a multi-launch one (logN >= 14 float2, >= 13 double2, <= 24) and
+ * batch * 2^logN * sizeof(element) <= 16 MiB, else TFFT_ERR_UNSUPPORTED / TFFT_ERR_TOO_LARGE.
+ * Calls no cudaMalloc/cudaFree.  The first call on a device looks up the arrays' device
+ * addresses; make that call before any stream capture.  All calls share the arrays, which
+ * keep the previous call's contents (every element that is read is written first, so
+ * nothing needs clearing); two calls whose kernels overlap on the GPU race -- issue them
+ * on one stream or synchronise in between. */
+int tfft_exec_static(int logN, long long batch, int dtype, const void* in, void* out, int device, void* stream);
+
 /* Last CUDA error code seen by any call on this plan (0 = none). */
 int tfft_last_cuda_error(tfft_plan plan);
 const char* tfft_status_string(int status);

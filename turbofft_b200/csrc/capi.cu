@@ -538,6 +538,181 @@ long long tfft_launch_count(void) { return g_launches.load(); }
 
 }  // extern "C"
 
+// ------------------------------------------------------------------------------------------
+// tfft_exec_static: the multi-launch transform with NO allocation anywhere on the call path.
+//
+// Multi-launch plans keep their intermediate result in a scratch buffer that
+// tfft_plan_create() obtains with cudaMalloc.  Some callers must not allocate at the time
+// they call -- code running inside a memory-pool-managed region, inside a latency-critical
+// loop that forbids driver allocation calls, or in a process whose device memory has been
+// handed out completely.  For them the scratch buffer and the twiddle tables live in two
+// file-scope __device__ arrays that every GPU loading this library holds from load to
+// exit: 16 MiB of scratch and 512 KiB of tables.
+//
+// In host code the names of those arrays are host-side stand-ins, not device addresses, so
+// the device address is looked up once per device with cudaGetSymbolAddress (with that
+// device current) and passed to the kernels like any other pointer.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 16u << 20;
+constexpr size_t kStaticTableBytes = 512u << 10;
+constexpr int kStaticMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
+
+struct StaticDeviceState {
+    bool ready = false;
+    void* scratch = nullptr;  // device address of g_static_scratch on this device
+    void* tables = nullptr;   // device address of g_static_tables on this device
+    int table_logn = -1;      // which (logN, dtype) the table region currently holds
+    int table_dtype = -1;
+    LaunchDesc L[3];
+    int n_launch = 0;
+};
+std::mutex g_static_mu;
+StaticDeviceState g_static_dev[kStaticMaxDevices];
+
+// Geometry and kernels of the launches of one built-in parameter row (FT off); the same
+// rules as tfft_plan_create(), without owning anything.
+int static_geometry(const ParamRow& row, int logN, long long batch, int dtype, LaunchDesc* L) {
+    long long outer = batch;
+    int log_rest = logN;
+    for (int i = 0; i < row.launches; ++i) {
+        LaunchDesc& d = L[i];
+        d = LaunchDesc();
+        d.logm = row.logni[i];
+        d.logc = ilog2_exact(row.bs[i]);
+        d.loge = ilog2_exact(row.n[i]);
+        if (d.loge > d.logm) d.loge = d.logm;
+        d.role = i == row.launches - 1 ? ROLE_LAST : ROLE_FIRST;
+        log_rest -= d.logm;
+        if (d.role == ROLE_FIRST) {
+            d.log_b = log_rest;
+            if (d.log_b < d.logc) d.logc = d.log_b;
+            d.n_tiles = outer << (d.log_b - d.logc);
+        } else {
+            d.log_n1 = row.logni[0];
+            d.log_q = row.launches == 3 ? row.logni[1] : 0;
+            if (d.log_n1 < d.logc) d.logc = d.log_n1;
+            d.n_tiles = (batch << (logN - d.logm)) >> d.logc;
+        }
+        outer <<= d.logm;
+        d.k = find_kernel(dtype, d.role, d.logm, d.loge, d.logc);
+        if (!d.k || !d.k->fn[FT_OFF]) return TFFT_ERR_UNSUPPORTED;
+        if (d.n_tiles > 2147483647LL) return TFFT_ERR_TOO_LARGE;
+        d.grid = (unsigned)d.n_tiles;
+    }
+    return TFFT_OK;
+}
+
+// Builds the twiddle tables of the launches on the host and copies them into the static
+// table region (stream ordered).  No allocation on the device.
+template <typename T>
+int static_upload_tables(StaticDeviceState& st, int logN, cudaStream_t stream) {
+    typedef typename Cplx<T>::type C;
+    size_t off = 0;
+    auto place = [&](const std::vector<C>& host, void** dev) -> int {
+        const size_t bytes = host.size() * sizeof(C);
+        if (off + bytes > kStaticTableBytes) return TFFT_ERR_TOO_LARGE;
+        *dev = (unsigned char*)st.tables + off;
+        // pageable source: the call returns once the data is staged, so `host` may go away
+        if (cudaMemcpyAsync(*dev, host.data(), bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return TFFT_ERR_CUDA;
+        off += (bytes + 255) & ~(size_t)255;
+        return TFFT_OK;
+    };
+    for (int i = 0; i < st.n_launch; ++i) {
+        LaunchDesc& d = st.L[i];
+        std::vector<C> t;
+        stage_twiddles(t, d.logm, d.loge);
+        int rc = place(t, &d.tw_st);
+        if (rc != TFFT_OK) return rc;
+        if (d.role == ROLE_FIRST) {
+            const int logp = d.logm + d.log_b;
+            d.tw_lo_bits = (logp + 1) / 2;
+            std::vector<C> lo, hi;
+            fill_twiddles(lo, 1LL << d.tw_lo_bits, 1, logp);
+            fill_twiddles(hi, 1LL << (logp - d.tw_lo_bits), 1LL << d.tw_lo_bits, logp);
+            if ((rc = place(lo, &d.tw_lo)) != TFFT_OK) return rc;
+            if ((rc = place(hi, &d.tw_hi)) != TFFT_OK) return rc;
+        }
+    }
+    (void)logN;
+    return TFFT_OK;
+}
+
+template <typename T>
+int static_launch(const StaticDeviceState& st, int logN, const void* in, void* out, cudaStream_t stream) {
+    typedef typename Cplx<T>::type C;
+    for (int i = 0; i < st.n_launch; ++i) {
+        const LaunchDesc& d = st.L[i];
+        KernelArgs<T> a;
+        memset(&a, 0, sizeof(a));
+        a.in = (const C*)(i == 0 ? in : st.scratch);
+        a.out = (C*)(i == st.n_launch - 1 ? out : st.scratch);
+        a.tw_st = (const C*)d.tw_st;
+        a.tw_lo = (const C*)d.tw_lo;
+        a.tw_hi = (const C*)d.tw_hi;
+        a.n_tiles = d.n_tiles;
+        a.tiles_per_cta = 1;
+        a.log_n = logN;
+        a.log_b = d.log_b;
+        a.log_n1 = d.log_n1;
+        a.log_q = d.log_q;
+        a.tw_lo_bits = d.tw_lo_bits;
+        a.inj_period = 1;
+        void* args[] = {&a};
+        if (cudaLaunchKernel(d.k->fn[FT_OFF], dim3(d.grid), dim3(d.k->threads), args, d.k->smem, stream) != cudaSuccess)
+            return TFFT_ERR_CUDA;
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return TFFT_OK;
+}
+
+}  // namespace
+
+extern "C" int tfft_exec_static(int logN, long long batch, int dtype, const void* in, void* out, int device,
+                                void* stream) {
+    if (!in || !out || batch < 1 || logN < 1 || logN > 24 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) ||
+        device < 0 || device >= kStaticMaxDevices)
+        return TFFT_ERR_BAD_ARG;
+    const size_t esize = dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2);
+    // the whole intermediate result must fit in the static scratch array
+    if (((unsigned long long)batch << logN) > kStaticScratchBytes / esize) return TFFT_ERR_TOO_LARGE;
+    std::vector<ParamRow> rows;
+    std::string err;
+    if (!parse_param_csv(builtin_param_csv(dtype), rows, err)) return TFFT_ERR_PARAM_FILE;
+    if ((int)rows.size() <= logN || rows[logN].launches < 2) return TFFT_ERR_UNSUPPORTED;  // 1-launch sizes use no scratch
+    if (!validate_row(rows[logN], err)) return TFFT_ERR_PARAM_FILE;
+
+    DeviceGuard guard(device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDeviceState& st = g_static_dev[device];
+    if (!st.ready) {
+        // once per device, with that device current: device addresses of the two arrays
+        if (cudaGetSymbolAddress(&st.scratch, g_static_scratch) != cudaSuccess) return TFFT_ERR_CUDA;
+        if (cudaGetSymbolAddress(&st.tables, g_static_tables) != cudaSuccess) return TFFT_ERR_CUDA;
+        st.ready = true;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    st.n_launch = rows[logN].launches;
+    int rc = static_geometry(rows[logN], logN, batch, dtype, st.L);
+    if (rc != TFFT_OK) return rc;
+    for (int i = 0; i < st.n_launch; ++i)
+        if (st.L[i].k->smem > 40 * 1024 &&
+            cudaFuncSetAttribute(st.L[i].k->fn[FT_OFF], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st.L[i].k->smem) !=
+                cudaSuccess)
+            return TFFT_ERR_CUDA;
+    // (re)fill the table region; it keeps the previous call's tables, so a call with the same
+    // (logN, dtype) could skip this, but the table pointers are recomputed either way
+    rc = dtype == TFFT_FLOAT2 ? static_upload_tables<float>(st, logN, s) : static_upload_tables<double>(st, logN, s);
+    if (rc != TFFT_OK) return rc;
+    st.table_logn = logN;
+    st.table_dtype = dtype;
+    return dtype == TFFT_FLOAT2 ? static_launch<float>(st, logN, in, out, s) : static_launch<double>(st, logN, in, out, s);
+}
+
 namespace tfft {
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace tfft
