@@ -37,7 +37,7 @@ L2_BYTES = 126 * 1024 * 1024
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--datatype", type=int, default=0, help="0 float2 (complex64), 1 double2 (complex128)")
@@ -146,7 +146,7 @@ def run_reference(a):
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML (read only)."""
 
-    def __init__(self, uuid, index, period=0.1):
+    def __init__(self, uuid, index, period=0.01):
         super().__init__(daemon=True)
         self.period = period
         self.samples, self.reasons, self.max_mhz = [], set(), None

@@ -62,9 +62,12 @@ int tfft_exec(tfft_plan plan, const void* in, void* out, void* stream);
 /* Same transform with HOST buffers: copies batch*N elements to the device, runs
  * tfft_exec and copies the result back, then synchronises.  Replaces the
  * cudaMemcpy pair around the launches in initializeData()/test_turbofft()
- * (initializeData.h:39, main.cu:72).  The device staging buffers are one grow-only
- * pair per device shared by all plans and kept until the library is unloaded;
- * calls are serialised. */
+ * (initializeData.h:39, main.cu:72).  Plans without FT whose batch spans at least
+ * three 64 MiB chunks are pipelined: chunks of whole signals are copied in,
+ * transformed and copied out on three internal streams so both PCIe directions
+ * overlap the kernels (use pinned host buffers).  Device staging buffers are
+ * grow-only per device, shared by all plans and kept until the library is
+ * unloaded; calls are serialised. */
 int tfft_exec_host(tfft_plan plan, const void* in_host, void* out_host, void* stream);
 
 /* Bytes of device memory the plan owns (tables + scratch + status). */

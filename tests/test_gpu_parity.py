@@ -135,6 +135,26 @@ def test_exec_host(torch_cuda):
     assert orc.rel_l2(y.numpy(), orc.fft_forward(xn)) <= orc.tolerance(np.complex64, 11)
 
 
+@pytest.mark.parametrize("dtype,logn,batch", [(0, 12, 7000), (1, 16, 200), (0, 20, 26)])
+def test_exec_host_pipelined(torch_cuda, dtype, logn, batch):
+    """Host buffers large enough for the chunked copy/compute/copy pipeline (>= 3 chunks of
+    64 MiB, ragged last chunk): same result as the device-pointer path."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    td = torch.complex64 if dtype == 0 else torch.complex128
+    g = torch.Generator().manual_seed(5)
+    x = torch.view_as_complex(torch.rand(batch, 1 << logn, 2, generator=g, dtype=torch.float32 if dtype == 0 else torch.float64) * 2 - 1)
+    x = x.to(td).pin_memory()
+    plan = tf.Plan(logn, batch, dtype)
+    y = plan.exec_host(x)
+    y_dev = plan(x.cuda()).cpu()
+    assert torch.equal(y, y_dev)
+    idx = [0, batch // 2, batch - 1]
+    ref = orc.fft_forward(x[idx].numpy())
+    assert orc.rel_l2(y[idx].numpy(), ref) <= orc.tolerance(CD[dtype], logn)
+
+
 def test_errors(torch_cuda):
     import turbofft_b200 as tf
 

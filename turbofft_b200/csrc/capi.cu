@@ -36,6 +36,15 @@ struct StagePair {
 std::mutex g_stage_mu;
 std::map<int, StagePair> g_stage;
 
+// Chunk-sized staging slots of the pipelined host path (3 in + 3 out per device).
+constexpr size_t kPipeChunkBytes = 64u << 20;
+struct PipeSlots {
+    void* in[3] = {nullptr, nullptr, nullptr};
+    void* out[3] = {nullptr, nullptr, nullptr};
+    size_t bytes = 0;
+};
+std::map<int, PipeSlots> g_pipe;
+
 struct LaunchDesc {
     int role = 0, logm = 0, loge = 0, logc = 0;
     const KernelEntry* k = nullptr;
@@ -82,6 +91,17 @@ struct tfft_plan_s {
     cudaStream_t last_stream = nullptr;
     int last_cuda_error = 0;
     std::vector<void*> allocs;
+    std::string param_csv;            // empty = built-in table
+    // host-buffer pipeline (tfft_exec_host): sub-plans for one chunk / the ragged last chunk,
+    // three internal streams and per-slot events
+    tfft_plan chunk_plan = nullptr;
+    tfft_plan tail_plan = nullptr;
+    long long chunk_batch = 0;
+    cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_in[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fft[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_out[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_start = nullptr;
     size_t esize() const { return dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2); }
 };
 
@@ -313,6 +333,7 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
     p->thread_bs = thread_bs;
     p->device = device;
     p->n_launch = row.launches;
+    if (param_csv && param_csv[0]) p->param_csv = param_csv;
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
 
     int status = TFFT_OK;
@@ -393,10 +414,90 @@ int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
     return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st) : launch_all<double>(p, in, out, st);
 }
 
+// Pipelined form of tfft_exec_host for plans without FT whose batch spans several chunks:
+// the batch is cut into chunks of whole signals (about 64 MiB); chunk i is copied in on one
+// stream, transformed on a second and copied out on a third, three slots deep, so the two
+// PCIe directions and the kernels overlap.  Returns TFFT_ERR_UNSUPPORTED when the plan does
+// not qualify (the caller then takes the plain path).
+static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host, cudaStream_t user) {
+    const size_t sig_bytes = ((size_t)1 << p->logn) * p->esize();
+    long long cb = (long long)(kPipeChunkBytes / sig_bytes);
+    if (p->if_ft || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
+    if (!p->chunk_plan) {
+        const char* csv = p->param_csv.empty() ? nullptr : p->param_csv.c_str();
+        int rc = tfft_plan_create(&p->chunk_plan, p->logn, cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
+        if (rc != TFFT_OK) return rc;
+        p->chunk_batch = cb;
+        if (p->batch % cb) {
+            rc = tfft_plan_create(&p->tail_plan, p->logn, p->batch % cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
+            if (rc != TFFT_OK) return rc;
+        }
+        for (int i = 0; i < 3; ++i) {
+            if (!cuda_ok(p, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking))) return TFFT_ERR_CUDA;
+            if (!cuda_ok(p, cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming)) ||
+                !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_fft[i], cudaEventDisableTiming)) ||
+                !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_out[i], cudaEventDisableTiming)))
+                return TFFT_ERR_CUDA;
+        }
+        if (!cuda_ok(p, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming))) return TFFT_ERR_CUDA;
+    }
+    cb = p->chunk_batch;
+    const size_t chunk_bytes = (size_t)cb * sig_bytes;
+    std::lock_guard<std::mutex> lock(g_stage_mu);
+    PipeSlots& ps = g_pipe[p->device];
+    if (ps.bytes < chunk_bytes) {
+        for (int i = 0; i < 3; ++i) {
+            if (ps.in[i]) cudaFree(ps.in[i]);
+            if (ps.out[i]) cudaFree(ps.out[i]);
+            ps.in[i] = ps.out[i] = nullptr;
+        }
+        ps.bytes = 0;
+        for (int i = 0; i < 3; ++i)
+            if (!cuda_ok(p, cudaMalloc(&ps.in[i], chunk_bytes)) || !cuda_ok(p, cudaMalloc(&ps.out[i], chunk_bytes)))
+                return TFFT_ERR_ALLOC;
+        ps.bytes = chunk_bytes;
+    }
+    cudaStream_t s_in = p->pipe_stream[0], s_fft = p->pipe_stream[1], s_out = p->pipe_stream[2];
+    // everything queued on the caller's stream so far comes first
+    if (!cuda_ok(p, cudaEventRecord(p->ev_start, user))) return TFFT_ERR_CUDA;
+    for (int i = 0; i < 3; ++i)
+        if (!cuda_ok(p, cudaStreamWaitEvent(p->pipe_stream[i], p->ev_start, 0))) return TFFT_ERR_CUDA;
+    const long long nchunk = (p->batch + cb - 1) / cb;
+    for (long long c = 0; c < nchunk; ++c) {
+        const int slot = (int)(c % 3);
+        const long long this_b = (c == nchunk - 1 && p->batch % cb) ? p->batch % cb : cb;
+        const size_t bytes = (size_t)this_b * sig_bytes;
+        const char* src = (const char*)in_host + (size_t)c * chunk_bytes;
+        char* dst = (char*)out_host + (size_t)c * chunk_bytes;
+        if (c >= 3) {
+            // slot reuse: its previous transform has consumed in[slot], its previous copy-out has drained out[slot]
+            if (!cuda_ok(p, cudaStreamWaitEvent(s_in, p->ev_fft[slot], 0))) return TFFT_ERR_CUDA;
+            if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, p->ev_out[slot], 0))) return TFFT_ERR_CUDA;
+        }
+        if (!cuda_ok(p, cudaMemcpyAsync(ps.in[slot], src, bytes, cudaMemcpyHostToDevice, s_in))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaEventRecord(p->ev_in[slot], s_in))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, p->ev_in[slot], 0))) return TFFT_ERR_CUDA;
+        const int rc = tfft_exec(this_b == cb ? p->chunk_plan : p->tail_plan, ps.in[slot], ps.out[slot], s_fft);
+        if (rc != TFFT_OK) return rc;
+        if (!cuda_ok(p, cudaEventRecord(p->ev_fft[slot], s_fft))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamWaitEvent(s_out, p->ev_fft[slot], 0))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaMemcpyAsync(dst, ps.out[slot], bytes, cudaMemcpyDeviceToHost, s_out))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaEventRecord(p->ev_out[slot], s_out))) return TFFT_ERR_CUDA;
+    }
+    for (int i = 0; i < 3; ++i)
+        if (!cuda_ok(p, cudaStreamSynchronize(p->pipe_stream[i]))) return TFFT_ERR_CUDA;
+    p->last_stream = s_fft;
+    return TFFT_OK;
+}
+
 int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* stream) {
     if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
+    {
+        const int rc = exec_host_pipelined(p, in_host, out_host, (cudaStream_t)stream);
+        if (rc != TFFT_ERR_UNSUPPORTED) return rc;
+    }
     const size_t bytes = ((size_t)p->batch << p->logn) * p->esize();
     std::lock_guard<std::mutex> lock(g_stage_mu);
     StagePair& sp = g_stage[p->device];
@@ -514,6 +615,15 @@ int tfft_ft_diag(tfft_plan p, int launch, double* diag, int cap_blocks) {
 int tfft_plan_destroy(tfft_plan p) {
     if (!p) return TFFT_ERR_BAD_ARG;
     DeviceGuard guard(p->device);
+    if (p->chunk_plan) tfft_plan_destroy(p->chunk_plan);
+    if (p->tail_plan) tfft_plan_destroy(p->tail_plan);
+    for (int i = 0; i < 3; ++i) {
+        if (p->pipe_stream[i]) cudaStreamDestroy(p->pipe_stream[i]);
+        if (p->ev_in[i]) cudaEventDestroy(p->ev_in[i]);
+        if (p->ev_fft[i]) cudaEventDestroy(p->ev_fft[i]);
+        if (p->ev_out[i]) cudaEventDestroy(p->ev_out[i]);
+    }
+    if (p->ev_start) cudaEventDestroy(p->ev_start);
     for (void* q : p->allocs) cudaFree(q);
     delete p;
     return TFFT_OK;
