@@ -51,6 +51,11 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-log-sample", type=int, default=24, help="log2 elements per sweep point in the CPU sample")
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "fourstep"],
+                    help="sweep: the logN+logBS=28 batch sweep (default); fourstep: ONE transform of 2^--logN points "
+                         "distributed over the GPUs (four-step, all-to-all over NVLink)")
+    ap.add_argument("--logN", type=int, default=30, help="fourstep: log2 of the transform length")
+    ap.add_argument("--natural", type=int, default=0, help="fourstep: 1 = natural-order output (third exchange)")
     return ap.parse_args()
 
 
@@ -401,10 +406,93 @@ def run_ours(a):
     return 0
 
 
+def run_fourstep(a):
+    """BASELINE config 5: one long transform over all GPUs of the node (world size >= 1)."""
+    import torch
+
+    import turbofft_b200 as tf
+    from turbofft_b200 import multi_gpu as mg
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    tdtype = torch.complex64 if a.datatype == 0 else torch.complex128
+    rdtype = torch.float32 if a.datatype == 0 else torch.float64
+    esize = 8 if a.datatype == 0 else 16
+    n_local = (1 << a.logN) // world
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    x = torch.view_as_complex(torch.rand(n_local, 2, generator=g, device=dev, dtype=rdtype) * 2 - 1).to(tdtype)
+    be = mg.DeviceBackend(a.datatype, local, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2), thread_bs=a.thread_bs)
+    fs = mg.FourStepFFT(a.logN, world, rank, be, natural_order=bool(a.natural))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(a.warmup, 3)):
+        y = fs(x)
+    barrier()
+    l0 = tf.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        y = fs(x)
+    e1.record()
+    barrier()
+    launches = tf.launch_count() - l0
+    ms = e0.elapsed_time(e1) / a.steps
+    ex = (x.real.double() ** 2 + x.imag.double() ** 2).sum()
+    ey = (y.real.double() ** 2 + y.imag.double() ** 2).sum()
+    stats = torch.stack([torch.tensor(ms, device=dev, dtype=torch.float64), ex, ey])
+    if dist is not None:
+        tmax = stats[:1].clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        sums = stats[1:].clone()
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+        ms, ex, ey = float(tmax[0]), float(sums[0]), float(sums[1])
+    else:
+        ms, ex, ey = float(stats[0]), float(stats[1]), float(stats[2])
+    nd, nc = be.ft_counts() if a.ft else (0, 0)
+    if rank == 0:
+        n = 1 << a.logN
+        peak, peak_src = peaks()
+        passes = 2  # two local FFT passes; each reads and writes the slab once at best
+        alg = 2.0 * n * esize / world
+        line = {
+            "metric": "four_step_c2c_fft_gflops", "value": 5.0 * n * a.logN / (ms * 1e-3) / 1e9, "unit": "GFLOPS",
+            "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32" if a.datatype == 0 else "f64", "data": "synthetic",
+            "config": {"workload": f"cfg5: one 2^{a.logN}-point C2C transform as 2^{fs.l1} x 2^{fs.l2}, four-step over "
+                                   f"{world} GPU(s), {'natural' if a.natural else 'transposed'} output, FT {'on' if a.ft else 'off'}",
+                       "exchanges": (3 if a.natural else 2) if world > 1 else 0,
+                       "nvlink_bytes_per_exchange_per_gpu": int((world - 1) / world * n * esize / world)},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                         "note": "algorithmic bytes = 2*N*sizeof/world per GPU; the local path makes %d FFT passes plus "
+                                 "pack/transpose passes" % passes},
+            "gpu_launches": int(launches), "check": {"parseval_rel_err": abs(ey / (n * ex) - 1.0)},
+            "ft": {"detected": nd, "corrected": nc} if a.ft else None,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     a = parse_args()
     if a.impl == "reference":
         return run_reference(a)
+    if a.workload == "fourstep":
+        return run_fourstep(a)
     return run_ours(a)
 
 
