@@ -376,7 +376,12 @@ def run_ours(a):
     dominant = max(per_point, key=lambda p: p["ms"])
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": None,
+        # DRAM bytes per step: every launch moves its whole batch once; ncu measured 0.95 x the
+        # algorithmic bytes per launch on 2^26-element cases (profiles/fft_kernel_fp32_logN16_two_launch.txt,
+        # ..._logN12_single_launch.txt), scaled here by elements and by the launches per step
+        "traffic": 0.95 * alg_bytes_point * sum(p["launches"] for p in per_point),
+        "traffic_note": "per step = 0.95 x algorithmic bytes per launch (ncu, 2^26-element captures, scaled) x launches per step",
+        "algorithmic_bytes_per_step": alg_bytes_point * len(points),
         "peak_source": peak_src, "stream_copy_gbs_same_run": copy_gbs, "frac_of_same_run_copy": achieved / copy_gbs,
         "kernel": "tfft::fft_kernel<T,LOGM,LOGE,LOGC,ROLE,FT> (every launch of the sweep is an instance)",
         "algorithmic_bytes_per_point": alg_bytes_point,
