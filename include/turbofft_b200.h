@@ -146,6 +146,24 @@ int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream);
  */
 int tfft_permute102(const void* src, void* dst, long long A, long long B, long long run_elems, int dtype,
                     void* stream);
+
+/* Fused exchange of the four-step transform: transpose (+ optional twiddle) of the local
+ * [rows][cols] matrix written straight into the receivers' buffers.  Element (i, c) goes to
+ * rank j = c / (cols / n_peers) at peer_dst[j][(c % (cols / n_peers)) * ld_dst + row0 + i],
+ * times exp(-2*pi*i*(row0 + i)*c / 2^log_total) if twiddle != 0.  peer_dst: host array of
+ * n_peers (<= 16) device pointers, the caller's own buffer at its own rank and peer
+ * mappings (tfft_peer_open) elsewhere.  rows, cols and cols / n_peers must be multiples of
+ * 32.  The stores are ordinary global stores over NVLink; the kernel does not wait for
+ * anybody -- order it against the receivers' next kernel with a stream-ordered barrier. */
+int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
+                           long long ld_dst, long long row0, int twiddle, int log_total, int dtype, void* stream);
+
+/* Receive buffers other processes can map: cudaMalloc + CUDA IPC handle (64 bytes). */
+int tfft_peer_alloc(size_t bytes, void** ptr);
+int tfft_peer_free(void* ptr);
+int tfft_peer_export(const void* ptr, void* handle64);
+int tfft_peer_open(const void* handle64, void** ptr);
+int tfft_peer_close(void* ptr);
 int tfft_transpose(const void* src, void* dst, long long rows, long long cols, int dtype, void* stream);
 int tfft_twiddle_transpose(const void* src, void* dst, long long rows, long long cols, long long row0,
                            long long col0, int log_total, int dtype, void* stream);

@@ -151,6 +151,24 @@ def test_helper_kernels(torch_cuda):
     assert torch.equal(src, dst)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,logn,natural", [(0, 16, False), (0, 19, True), (1, 14, True), (1, 18, False)])
+def test_fused_four_step_single_gpu(torch_cuda, dtype, logn, natural):
+    """World size 1: the fused scatter-transpose kernels store into this GPU's own buffers."""
+    torch = torch_cuda
+    npdt = np.complex64 if dtype == 0 else np.complex128
+    x = orc.make_input(1, 1 << logn, npdt, seed=logn)[0]
+    fs = mg.FusedFourStepFFT(logn, 1, 0, dtype, 0, natural_order=natural, if_ft=1)
+    y = fs(torch.from_numpy(x).cuda()).cpu().numpy()
+    y2 = fs(torch.from_numpy(x).cuda()).cpu().numpy()     # buffers reused by a second call
+    fs.close()
+    ref = orc.fft_forward(x)
+    if not natural:
+        ref = ref.reshape(fs.n2, fs.n1).T.reshape(-1)
+    assert orc.rel_l2(y, ref) <= orc.tolerance(npdt, logn)
+    assert np.array_equal(y, y2)
+
+
 def _gpu_worker(rank, world, port, logn, dtype, q):
     import torch
     import torch.distributed as dist
@@ -164,9 +182,18 @@ def _gpu_worker(rank, world, port, logn, dtype, q):
         n = 1 << logn
         x = orc.make_input(1, n, npdt, seed=7)[0]
         b, e = mg.shard_range(n, world, rank)
+        ref = orc.fft_forward(x)[b:e]
         fs = mg.FourStepFFT(logn, world, rank, mg.DeviceBackend(dtype, rank, if_ft=1), natural_order=True)
         y = fs(torch.from_numpy(x[b:e].copy()).cuda()).cpu().numpy()
-        q.put((rank, orc.rel_l2(y, orc.fft_forward(x)[b:e])))
+        # the same transform with the exchanges fused into peer-storing kernels, twice in a row
+        fused = mg.FusedFourStepFFT(logn, world, rank, dtype, rank, natural_order=True, if_ft=1)
+        xg = torch.from_numpy(x[b:e].copy()).cuda()
+        yf = fused(xg).cpu().numpy()
+        yf2 = fused(xg).cpu().numpy()
+        torch.cuda.synchronize()
+        dist.barrier()
+        fused.close()
+        q.put((rank, max(orc.rel_l2(y, ref), orc.rel_l2(yf, ref), orc.rel_l2(yf2, ref))))
     finally:
         dist.destroy_process_group()
 

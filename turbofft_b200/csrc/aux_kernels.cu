@@ -3,6 +3,8 @@
 // (twiddled) transposes the multi-GPU four-step transform is assembled from.
 #include <cuda_runtime.h>
 
+#include <cstring>
+
 #include "../../include/turbofft_b200.h"
 #include "registry.h"
 
@@ -76,6 +78,55 @@ __global__ void __launch_bounds__(256) permute102_kernel(const uint4* __restrict
     }
 }
 
+// Fused "transpose + all-to-all + unpack" of the multi-GPU four-step transform: element
+// (i, c) of the local row-major matrix src[rows][cols] goes to rank j = c / cb, into that
+// rank's buffer dst[j] at [(c % cb) * ld + row0 + i] -- the transposed position in the
+// receiver's layout -- optionally multiplied by exp(-2*pi*i*(row0 + i)*c / 2^log_total).
+// dst[j] are device pointers (this GPU's own buffer for j == rank, peer mappings otherwise);
+// the stores are plain coalesced st.global over NVLink, 32 consecutive elements per row of a
+// tile.  Completion on the receivers is established by the caller (a stream-ordered barrier
+// after the kernel); this kernel never waits on a peer.
+constexpr int kMaxPeers = 16;
+template <typename C>
+struct PeerPtrs {
+    C* p[kMaxPeers];
+};
+
+template <typename C, bool TW>
+__global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restrict__ src, PeerPtrs<C> dst, long long rows,
+                                                                long long cols, long long cb, long long ld, long long row0,
+                                                                int log_total) {
+    __shared__ C tile[32][33];
+    const long long tiles_c = cols / 32;
+    const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long r = tr * 32 + ty + 8 * k, c = tc * 32 + tx;
+        C v = __ldcs(src + r * cols + c);
+        if (TW) {
+            typedef typename RealOf<C>::type T;
+            const unsigned long long mask = (1ULL << log_total) - 1;
+            const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)c) & mask;
+            double sn, cs;
+            sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
+            C w;
+            w.x = (T)(v.x * cs - v.y * sn);
+            w.y = (T)(v.x * sn + v.y * cs);
+            v = w;
+        }
+        tile[ty + 8 * k][tx] = v;
+    }
+    __syncthreads();
+    const long long c0 = tc * 32;
+    C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb is a multiple of 32
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long c = c0 + ty + 8 * k;
+        base[(c % cb) * ld + row0 + tr * 32 + tx] = tile[tx][ty + 8 * k];
+    }
+}
+
 template <bool TW>
 int launch_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
                      int log_total, int dtype, void* stream) {
@@ -123,6 +174,55 @@ int tfft_permute102(const void* src, void* dst, long long A, long long B, long l
     tfft::note_launch();
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
 }
+
+int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
+                           long long ld_dst, long long row0, int twiddle, int log_total, int dtype, void* stream) {
+    if (!src || !peer_dst || n_peers < 1 || n_peers > kMaxPeers || rows < 32 || cols < 32 || (rows & 31) || (cols & 31) ||
+        cols % n_peers || ((cols / n_peers) & 31) || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
+        return TFFT_ERR_BAD_ARG;
+    if (twiddle && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
+    const long long blocks = (rows / 32) * (cols / 32);
+    if (blocks > 2147483647LL) return TFFT_ERR_TOO_LARGE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long cb = cols / n_peers;
+    if (dtype == TFFT_FLOAT2) {
+        PeerPtrs<float2> pp;
+        for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (float2*)(i < n_peers ? peer_dst[i] : nullptr);
+        if (twiddle)
+            scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+        else
+            scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+    } else {
+        PeerPtrs<double2> pp;
+        for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (double2*)(i < n_peers ? peer_dst[i] : nullptr);
+        if (twiddle)
+            scatter_transpose_kernel<double2, true><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+        else
+            scatter_transpose_kernel<double2, false><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+    }
+    tfft::note_launch();
+    return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+// Peer-visible device buffers for the fused exchange: plain cudaMalloc so that the IPC
+// handle refers to the start of the buffer.
+int tfft_peer_alloc(size_t bytes, void** ptr) {
+    if (!ptr || !bytes) return TFFT_ERR_BAD_ARG;
+    return cudaMalloc(ptr, bytes) == cudaSuccess ? TFFT_OK : TFFT_ERR_ALLOC;
+}
+int tfft_peer_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA; }
+int tfft_peer_export(const void* ptr, void* handle64) {
+    if (!ptr || !handle64) return TFFT_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    return cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle64, (void*)ptr) == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+int tfft_peer_open(const void* handle64, void** ptr) {
+    if (!ptr || !handle64) return TFFT_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+int tfft_peer_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA; }
 
 int tfft_transpose(const void* src, void* dst, long long rows, long long cols, int dtype, void* stream) {
     return launch_transpose<false>(src, dst, rows, cols, 0, 0, 1, dtype, stream);

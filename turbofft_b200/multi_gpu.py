@@ -151,3 +151,140 @@ class FourStepFFT:
     def output_index(self, k1_local: int, k2: int) -> int:
         """Global frequency index of element [k1_local][k2] of the transposed-out result."""
         return (self.rank * (self.n1 // self.world) + k1_local) + self.n1 * k2
+
+
+class PeerBuffers:
+    """Two receive buffers per rank that every other rank of the node can store into.
+
+    Allocated with tfft_peer_alloc (plain cudaMalloc, so the CUDA IPC handle points at the
+    start), handles exchanged with one all_gather, peers mapped with tfft_peer_open.
+    """
+
+    def __init__(self, nbytes: int, world: int, rank: int, device_index: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.world, self.rank, self.nbytes = world, rank, nbytes
+        self.local = []
+        self.peers = []   # per buffer: list of `world` pointers
+        self._opened = []
+        for _ in range(2):
+            p = C.c_void_p()
+            _lib.check(lib().tfft_peer_alloc(nbytes, C.byref(p)), "tfft_peer_alloc")
+            self.local.append(p.value)
+        for b in range(2):
+            ptrs = [None] * world
+            ptrs[rank] = self.local[b]
+            if world > 1:
+                h = (C.c_ubyte * 64)()
+                _lib.check(lib().tfft_peer_export(self.local[b], h), "tfft_peer_export")
+                mine = torch.tensor(list(h), dtype=torch.uint8, device=f"cuda:{device_index}")
+                allh = torch.empty(world * 64, dtype=torch.uint8, device=mine.device)
+                dist.all_gather_into_tensor(allh, mine, group=group)
+                allh = allh.cpu().numpy().reshape(world, 64)
+                for j in range(world):
+                    if j == rank:
+                        continue
+                    hb = (C.c_ubyte * 64)(*allh[j].tolist())
+                    q = C.c_void_p()
+                    _lib.check(lib().tfft_peer_open(hb, C.byref(q)), "tfft_peer_open")
+                    ptrs[j] = q.value
+                    self._opened.append(q.value)
+            self.peers.append(ptrs)
+        if world > 1:
+            dist.barrier(group=group)
+
+    def table(self, b: int):
+        return (C.c_void_p * self.world)(*self.peers[b])
+
+    def close(self):
+        for q in self._opened:
+            lib().tfft_peer_close(q)
+        self._opened = []
+        for p in self.local:
+            lib().tfft_peer_free(p)
+        self.local = []
+
+
+class FusedFourStepFFT(FourStepFFT):
+    """Four-step transform whose exchanges are fused into the transposing kernels.
+
+    Each all-to-all of FourStepFFT, together with the pack before it and the transpose after
+    it, becomes ONE kernel (tfft_scatter_transpose) that applies the twiddle, transposes
+    through shared memory and stores every tile straight into the receiving GPU's buffer over
+    NVLink; a one-element all_reduce behind it orders the receivers' next kernel after all
+    senders.  Local HBM passes per transform drop from ten to six and the transfer overlaps
+    the kernel that produces the data.  Same input and output conventions as FourStepFFT.
+    """
+
+    def __init__(self, logn: int, world: int, rank: int, dtype_code: int, device_index: int, group=None,
+                 natural_order: bool = False, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1):
+        import torch
+
+        be = DeviceBackend(dtype_code, device_index, if_ft, if_err, thread_bs)
+        super().__init__(logn, world, rank, be, group, natural_order)
+        if (self.n1 // world) % 32 or (self.n2 // world) % 32:
+            raise ValueError("each rank's share of both factors must be a multiple of 32")
+        self.torch, self.dt, self.dev = torch, dtype_code, device_index
+        self.esize = 8 if dtype_code == 0 else 16
+        self.bufs = PeerBuffers((self.n1 * self.n2 // world) * self.esize, world, rank, device_index, group)
+        self.token = torch.zeros(1, device=f"cuda:{device_index}")
+        self._plans = {}
+
+    def _stream(self):
+        return self.torch.cuda.current_stream(self.dev).cuda_stream
+
+    def _fence(self):
+        # stream-ordered barrier: nobody's next kernel starts before everybody's stores are issued and complete
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(self.token, group=self.group)
+
+    def _scatter(self, src_ptr, buf, rows, cols, ld, row0, tw):
+        _lib.check(lib().tfft_scatter_transpose(src_ptr, self.bufs.table(buf), self.world, rows, cols, ld, row0, int(tw),
+                                                self.logn, self.dt, self._stream()), "tfft_scatter_transpose")
+
+    def _fft_from(self, src_ptr, logn, count, out):
+        from . import Plan
+
+        key = (logn, count)
+        if key not in self._plans:
+            self._plans[key] = Plan(logn, count, self.dt, self.be.if_ft, self.be.if_err, self.be.thread_bs, device=self.dev)
+        self._plans[key].exec_ptr(src_ptr, out.data_ptr(), self._stream())
+        return out
+
+    def __call__(self, x_local):
+        P, r = self.world, self.rank
+        n1, n2, n1l, n2l = self.n1, self.n2, self.n1 // P, self.n2 // P
+        x_local = x_local.contiguous()
+        # 1. x[n1l][N2] -> every rank's buffer 0 as [n2l][N1]
+        self._scatter(x_local.data_ptr(), 0, n1l, n2, n1, r * n1l, False)
+        self._fence()
+        # 2. FFT over n1
+        tmp = self._fft_from(self.bufs.local[0], self.l1, n2l, self.torch.empty_like(x_local))
+        # 3. twiddle W_N^(n2*k1) + transpose -> every rank's buffer 1 as [n1l][N2]
+        self._scatter(tmp.data_ptr(), 1, n2l, n1, n2, r * n2l, True)
+        self._fence()
+        # 4. FFT over n2 -> Z[k1_local][k2]
+        out = self._fft_from(self.bufs.local[1], self.l2, n1l, tmp)
+        if not self.natural:
+            return out
+        self._scatter(out.data_ptr(), 0, n1l, n2, n1, r * n1l, False)
+        self._fence()
+        res = self.torch.empty_like(x_local)
+        # device-to-device copy of this rank's slab out of the receive buffer (stream ordered)
+        _lib.check(lib().tfft_stream_copy(self.bufs.local[0], res.data_ptr(), res.numel() * self.esize, self._stream()),
+                   "tfft_stream_copy")
+        return res
+
+    def ft_counts(self):
+        nd = nc = 0
+        for p in self._plans.values():
+            d, c, _ = p.ft_status()
+            nd += d
+            nc += c
+        return nd, nc
+
+    def close(self):
+        self.bufs.close()
