@@ -197,7 +197,11 @@ struct Cfg {
     static constexpr int PADSHIFT = L::PADSHIFT;
     static constexpr int MPAD = (M - 1) + ((M - 1) >> PADSHIFT) + 1;
     static constexpr int PITCH = MPAD + L::EXTRA;
-    static constexpr int SMEM_ELEMS = S > 1 ? (LAYOUT_COLS ? MPAD * C : PITCH * C) : 0;
+    // One thread per line (M == E, whole signals): lines are too short to be read coalesced
+    // by their owner, so the tile -- contiguous in memory -- is staged through shared memory:
+    // cooperative coalesced copy in, each thread picks up its line (pitch M + 1), and back.
+    static constexpr bool STAGED_IO = (ROLE == ROLE_SINGLE && S == 1 && TPL == 1 && LOGM >= 2);
+    static constexpr int SMEM_ELEMS = STAGED_IO ? (M + 1) * C : (S > 1 ? (LAYOUT_COLS ? MPAD * C : PITCH * C) : 0);
     static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
     // Occupancy target handed to the compiler as the register cap: enough blocks for
     // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
@@ -304,7 +308,7 @@ struct Fft {
 
     // Final stage: natural-order outputs, right checksum, inter-launch twiddle, store.
     template <int LR, bool DO_FT>
-    static __device__ __forceinline__ void finish(C (&v)[E], const KernelArgs<T>& a, const Geom& g, int s, int c,
+    static __device__ __forceinline__ void finish(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g, int s, int c,
                                                   const FtRegs& f, T& tout) {
         constexpr int R = 1 << LR, NB = E / R;
         C y[E];
@@ -352,7 +356,19 @@ struct Fft {
                 y[i] = cmul(y[i], w);
             }
         }
-        if (c < g.ncols) {
+        if constexpr (K::STAGED_IO) {
+            // every thread only touches its own line here, so no barrier is needed before
+#pragma unroll
+            for (int i = 0; i < E; ++i) sm[c * (K::M + 1) + i] = y[i];
+            __syncthreads();
+            const long long valid = (long long)g.ncols << LOGM;
+            C* dst = a.out + g.out_base;
+#pragma unroll
+            for (int k = 0; k < K::M; ++k) {
+                const int fl = k * K::C + (int)threadIdx.x;
+                if (fl < valid) dst[fl] = sm[(fl >> LOGM) * (K::M + 1) + (fl & (K::M - 1))];
+            }
+        } else if (c < g.ncols) {
             C* dst = a.out + g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
 #pragma unroll
             for (int i = 0; i < E; ++i) dst[(long long)i * TPL * g.out_rs] = y[i];
@@ -405,7 +421,7 @@ struct Fft {
             __syncthreads();
             stage<ST + 1, DO_FT>(v, sm, a, g, f, tout);
         } else {
-            finish<LR, DO_FT>(v, a, g, s, c, f, tout);
+            finish<LR, DO_FT>(v, sm, a, g, s, c, f, tout);
         }
     }
 
@@ -418,7 +434,23 @@ struct Fft {
         int s, c;
         map_thread<K::CFAST_IN>(s, c);
         C v[E];
-        if (c < g.ncols) {
+        if constexpr (K::STAGED_IO) {
+            // flat element f of the tile = line f / M, row f % M; consecutive threads, consecutive f
+            const long long valid = (long long)g.ncols << LOGM;
+            const C* src = a.in + g.in_base;
+            __syncthreads();  // previous tile's copy-out has finished reading shared memory
+#pragma unroll
+            for (int k = 0; k < K::M; ++k) {
+                const int fl = k * K::C + (int)threadIdx.x;
+                C t;
+                t.x = t.y = T(0);
+                if (fl < valid) t = src[fl];
+                sm[(fl >> LOGM) * (K::M + 1) + (fl & (K::M - 1))] = t;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = sm[c * (K::M + 1) + i];
+        } else if (c < g.ncols) {
             const C* src = a.in + g.in_base + (long long)c * g.in_cs + (long long)s * g.in_rs;
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i] = src[(long long)i * TPL * g.in_rs];
