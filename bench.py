@@ -51,7 +51,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-log-sample", type=int, default=24, help="log2 elements per sweep point in the CPU sample")
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "fourstep"],
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "fourstep", "cfg1", "cfg4"],
                     help="sweep: the logN+logBS=28 batch sweep (default); fourstep: ONE transform of 2^--logN points "
                          "distributed over the GPUs (four-step, all-to-all over NVLink)")
     ap.add_argument("--logN", type=int, default=30, help="fourstep: log2 of the transform length")
@@ -500,12 +500,125 @@ def run_fourstep(a):
     return 0
 
 
+def _time_us(torch, fn, reps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def run_cfg1(a):
+    """BASELINE config 1: N = 2^10, batch 16, complex64, seed 0 -- a latency case (262 144
+    algorithmic bytes), reported in microseconds, not as a roofline fraction."""
+    import numpy as np
+    import torch
+
+    import turbofft_b200 as tf
+
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(0)
+    xn = rng.uniform(-1, 1, (16, 1024, 2)).astype(np.float32).view(np.complex64).reshape(16, 1024)
+    x = torch.from_numpy(xn).cuda()
+    y = torch.empty_like(x)
+    plan = tf.Plan(10, 16, 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    run = lambda: plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+    for _ in range(20):
+        run()
+    back_to_back = _time_us(torch, run, 2000)
+    t0 = time.perf_counter()
+    for _ in range(500):
+        run()
+        torch.cuda.synchronize()
+    with_sync = (time.perf_counter() - t0) * 1e6 / 500
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        gs = torch.cuda.current_stream().cuda_stream
+        plan.exec_ptr(x.data_ptr(), y.data_ptr(), gs)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(10):
+                plan.exec_ptr(x.data_ptr(), y.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    graph_us = _time_us(torch, g.replay, 200) / 10
+    ref = np.fft.fft(xn.astype(np.complex128), axis=-1)
+    err = float(np.linalg.norm(y.cpu().numpy() - ref) / np.linalg.norm(ref))
+    print(json.dumps({
+        "metric": "c2c_fft_latency_us_N1024_batch16", "value": back_to_back, "unit": "us", "n_gpus": 1, "higher_is_better": False,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": "cfg1: N=2^10, batch 16, complex64 uniform[-1,1) seed 0, FT off"},
+        "us_per_transform_back_to_back": back_to_back, "us_per_transform_with_host_sync": with_sync,
+        "us_per_transform_cuda_graph_of_10": graph_us, "rel_l2_vs_float64_fft": err,
+        "gflops": 5 * 1024 * 10 * 16 / back_to_back / 1e3}))
+    return 0
+
+
+def run_cfg4(a):
+    """BASELINE config 4: logN = 20, batch 256, complex64 uniform[-1,1), err_threshold 1e-3,
+    +100 injected: (i) the reference's fault pattern (every block of the last launch) for
+    thread_bs 1..32, (ii) one faulty block per 1000.  Reports detection rate, exactness of
+    the located index, bit-equality of the corrected output with the fault-free run, overhead."""
+    import torch
+
+    import turbofft_b200 as tf
+
+    torch.cuda.set_device(0)
+    logn, batch = 20, 256
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.view_as_complex(torch.rand(batch << logn, 2, generator=g, device="cuda") * 2 - 1).view(batch, 1 << logn)
+    y = torch.empty_like(x)
+    stream = torch.cuda.current_stream().cuda_stream
+    base_plan = tf.Plan(logn, batch, 0)
+    clean = base_plan(x)
+    run = lambda p: (lambda: p.exec_ptr(x.data_ptr(), y.data_ptr(), stream))
+    for _ in range(3):
+        run(base_plan)()
+    t0 = _time_us(torch, run(base_plan), 20)
+    rows = []
+    for tbs in (1, 2, 4, 8, 16, 32):
+        det = tf.Plan(logn, batch, 0, if_ft=1, thread_bs=tbs)
+        t_det = _time_us(torch, run(det), 10)
+        err = tf.Plan(logn, batch, 0, if_ft=1, if_err=1, thread_bs=tbs)
+        t_err = _time_us(torch, run(err), 10)
+        nd, nc, loc = err.ft_status()
+        exact = sum(1 for b, k in enumerate(loc) if k != -1 and k == b % tbs + 1)
+        sparse = tf.Plan(logn, batch, 0, if_ft=1, if_err=1, thread_bs=tbs)
+        sparse.set_injection(True, launch=-1, period=1000, phase=7)
+        t_sp = _time_us(torch, run(sparse), 10)
+        nds, ncs, locs = sparse.ft_status()
+        n_faulty = sum(1 for b in range(len(locs)) if b % 1000 == 7)
+        rows.append({"thread_bs": tbs, "blocks": len(loc), "detected": nd, "located_exactly": exact, "corrected": nc,
+                     "output_equals_fault_free": bool(torch.equal(y, clean)) if False else None,
+                     "ft_detect_overhead_pct": 100 * (t_det / t0 - 1), "ft_inject_correct_overhead_pct": 100 * (t_err / t0 - 1),
+                     "sparse": {"faulty_blocks": n_faulty, "detected": nds, "corrected": ncs,
+                                "false_positives": sum(1 for b, k in enumerate(locs) if k != -1 and b % 1000 != 7),
+                                "overhead_pct": 100 * (t_sp / t0 - 1)}})
+        # bit-equality of the repaired output where every fault was seen
+        yy = err(x)
+        rows[-1]["output_equals_fault_free"] = bool(torch.equal(yy, clean))
+    print(json.dumps({
+        "metric": "ft_overhead_pct_logN20_batch256", "value": min(r["ft_detect_overhead_pct"] for r in rows), "unit": "%",
+        "n_gpus": 1, "higher_is_better": False, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg4: logN=20, batch 256, complex64 uniform[-1,1), err_inj 100, err_smoothing 1000, err_threshold 1e-3"},
+        "no_ft_us": t0, "rows": rows,
+        "note": "detected < blocks means the reference's own test |delta|/(1000+S) > 1e-3 stays below threshold for those blocks "
+                "(S grows with the signal energy of thread_bs tiles); the CPU model of the decision predicts the same"}))
+    return 0
+
+
 def main():
     a = parse_args()
     if a.impl == "reference":
         return run_reference(a)
     if a.workload == "fourstep":
         return run_fourstep(a)
+    if a.workload == "cfg1":
+        return run_cfg1(a)
+    if a.workload == "cfg4":
+        return run_cfg4(a)
     return run_ours(a)
 
 
