@@ -115,7 +115,8 @@ int tfft_plan_destroy(tfft_plan plan);
  * service loops, devices whose memory is fully handed out).  Runs the built-in multi-launch
  * plan for (logN, dtype), FT off, with the intermediate buffer and the twiddle tables in
  * static device arrays of the library (16 MiB + 512 KiB held by every GPU that loads it).
- * Limits: the size must be a multi-launch one (logN >= 14 float2, >= 13 double2, <= 24) and
+ * Limits: the size must be a multi-launch one of the built-in table (currently logN >= 15
+ * float2, >= 14 double2; at most 24) and
  * batch * 2^logN * sizeof(element) <= 16 MiB, else TFFT_ERR_UNSUPPORTED / TFFT_ERR_TOO_LARGE.
  * Calls no cudaMalloc/cudaFree.  The first call on a device looks up the arrays' device
  * addresses; make that call before any stream capture.  All calls share the arrays, which

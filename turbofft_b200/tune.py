@@ -19,7 +19,7 @@ import tempfile
 
 from . import planner
 
-MAX_SMEM = 110 * 1024
+MAX_SMEM = 200 * 1024
 
 
 def _row(logn, parts):
