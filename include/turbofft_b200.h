@@ -84,6 +84,13 @@ int tfft_plan_info(tfft_plan plan, int* info);
  * as run-time values.  Defaults: 100, 1000, 1e-3. */
 int tfft_set_ft_params(tfft_plan plan, double err_inj, double err_smoothing, double err_threshold);
 
+/* Direction and normalisation (no counterpart in the reference, which is forward and
+ * unnormalised only).  inverse != 0 computes scale * conj(F(conj(x))), i.e. the inverse DFT
+ * for scale = 1/N; inverse == 0 computes scale * F(x).  The conjugations and the scaling
+ * ride on the first launch's loads and the last launch's stores; FT checksums are taken on
+ * the conjugated data and are unaffected.  Default: forward, scale 1. */
+int tfft_set_direction(tfft_plan plan, int inverse, double scale);
+
 /* Fault site selection.  The reference injects into every block of the last
  * launch (fft_codegen.py:412-415): that is launch = -1, period = 1, phase = 0
  * and is the default when the plan was created with if_err.  period > 1 hits

@@ -124,6 +124,32 @@ def test_torch_entry_point(torch_cuda):
     assert orc.rel_l2(y32.cpu().numpy(), ref32) <= 1.1e-5
 
 
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn,batch", [(3, 100), (8, 33), (12, 4), (13, 3), (16, 4), (23, 1)])
+def test_inverse_and_norms(torch_cuda, logn, batch, dtype):
+    """ifft and the torch-style norms: round trip and agreement with numpy's conventions."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    xn = orc.make_input(batch, 1 << logn, CD[dtype], seed=logn)
+    x = torch.from_numpy(xn).cuda()
+    tol = orc.tolerance(CD[dtype], logn)
+    xi = tf.ifft(x).cpu().numpy()
+    assert orc.rel_l2(xi, np.fft.ifft(xn.astype(np.complex128), axis=-1)) <= tol
+    back = tf.ifft(tf.fft(x)).cpu().numpy()
+    assert orc.rel_l2(back, xn) <= 2 * tol
+    for norm in ("ortho", "forward"):
+        assert orc.rel_l2(tf.fft(x, norm=norm).cpu().numpy(), np.fft.fft(xn.astype(np.complex128), axis=-1, norm=norm)) <= tol
+        assert orc.rel_l2(tf.ifft(x, norm=norm).cpu().numpy(), np.fft.ifft(xn.astype(np.complex128), axis=-1, norm=norm)) <= tol
+    # the FT kernels take the same direction flags and stay quiet on clean data
+    plan = tf.Plan(logn, batch, dtype, if_ft=1, if_err=1, thread_bs=2)
+    plan.set_injection(False)
+    plan.set_direction(True, 1.0 / (1 << logn))
+    y_ft = plan(x).cpu().numpy()
+    assert orc.rel_l2(y_ft, np.fft.ifft(xn.astype(np.complex128), axis=-1)) <= tol
+    assert plan.ft_status()[0] == 0
+
+
 def test_exec_host(torch_cuda):
     import turbofft_b200 as tf
 

@@ -14,7 +14,7 @@ from typing import Optional
 from . import _lib
 from ._lib import TurboFFTError, lib
 
-__all__ = ["Plan", "fft", "TurboFFTError", "lib", "stream_copy", "launch_count"]
+__all__ = ["Plan", "fft", "ifft", "TurboFFTError", "lib", "stream_copy", "launch_count"]
 
 FLOAT2, DOUBLE2 = 0, 1
 
@@ -95,6 +95,10 @@ class Plan:
     def workspace_bytes(self) -> int:
         return int(lib().tfft_workspace_bytes(self._h))
 
+    def set_direction(self, inverse: bool = False, scale: float = 1.0):
+        """inverse: scale * conj(F(conj(x))) (the inverse DFT for scale = 1/N); else scale * F(x)."""
+        _lib.check(lib().tfft_set_direction(self._h, int(inverse), float(scale)), "tfft_set_direction")
+
     # -- fault tolerance
     def set_ft_params(self, err_inj: float = 100.0, err_smoothing: float = 1000.0, err_threshold: float = 1e-3):
         _lib.check(lib().tfft_set_ft_params(self._h, err_inj, err_smoothing, err_threshold), "tfft_set_ft_params")
@@ -137,11 +141,16 @@ class Plan:
 _plan_cache = {}
 
 
-def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None):
-    """Forward unnormalised FFT along the last axis of a complex64/complex128 CUDA tensor.
+_NORM_FWD = {None: 0.0, "backward": 0.0, "ortho": -0.5, "forward": -1.0}  # exponent of N in the forward scale
+
+
+def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None, inverse: bool = False):
+    """FFT along the last axis of a complex64/complex128 CUDA tensor (forward, unnormalised by
+    default, which is the reference's transform).
 
     Power-of-two lengths 2..2^30; leading axes are the batch.  ft/err are the
-    reference's --if_ft / --if_err.  Plans are cached per (device, shape, mode).
+    reference's --if_ft / --if_err.  norm follows torch.fft ("backward", "ortho", "forward");
+    inverse=True is what ifft() calls.  Plans are cached per (device, shape, mode).
     """
     if not x.is_cuda:
         raise ValueError("turbofft_b200.fft needs a CUDA tensor: there is no CPU path")
@@ -150,13 +159,22 @@ def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None):
     if n < 2 or (1 << logn) != n:
         raise ValueError("last axis must be a power of two >= 2")
     batch = x.numel() // n
-    key = (x.device.index, logn, batch, _dtype_code(x.dtype), bool(ft), bool(err), thread_bs)
+    if norm not in _NORM_FWD:
+        raise ValueError(f"unknown norm {norm!r}")
+    expo = _NORM_FWD[norm] if not inverse else -1.0 - _NORM_FWD[norm]
+    key = (x.device.index, logn, batch, _dtype_code(x.dtype), bool(ft), bool(err), thread_bs, bool(inverse), expo)
     plan = _plan_cache.get(key)
     if plan is None:
         plan = Plan(logn, batch, _dtype_code(x.dtype), int(ft or err), int(err), thread_bs, device=x.device.index)
+        plan.set_direction(inverse, float(n) ** expo)
         _plan_cache[key] = plan
     y = plan(x.reshape(batch, n), out=None if out is None else out.reshape(batch, n))
     return y.reshape(x.shape)
+
+
+def ifft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None):
+    """Inverse FFT along the last axis (1/N scaling by default, as torch.fft.ifft)."""
+    return fft(x, ft=ft, err=err, thread_bs=thread_bs, out=out, norm=norm, inverse=True)
 
 
 def stream_copy(src, dst) -> None:

@@ -88,6 +88,8 @@ struct tfft_plan_s {
     double err_threshold = TFFT_DEFAULT_ERR_THRESHOLD;
     int inj_enable = 0, inj_launch = -1, inj_period = 1, inj_phase = 0;
     int diag = 0;
+    int inverse = 0;     // 0: forward; 1: conjugate in, conjugate out (inverse transform)
+    double scale = 1.0;  // applied with the conjugation of the last launch
     cudaStream_t last_stream = nullptr;
     int last_cuda_error = 0;
     std::vector<void*> allocs;
@@ -278,6 +280,10 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         a.log_n1 = d.log_n1;
         a.log_q = d.log_q;
         a.tw_lo_bits = d.tw_lo_bits;
+        a.conj_in = (p->inverse && i == 0) ? 1 : 0;
+        a.scale_out = ((p->inverse || p->scale != 1.0) && i == p->n_launch - 1) ? 1 : 0;
+        a.scale_x = (T)p->scale;
+        a.scale_y = (T)(p->inverse ? -p->scale : p->scale);
         a.inj_on = (p->if_err && p->inj_enable && i == inj_launch) ? 1 : 0;
         a.inj_period = p->inj_period;
         a.inj_phase = p->inj_phase;
@@ -432,6 +438,7 @@ static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host,
             rc = tfft_plan_create(&p->tail_plan, p->logn, p->batch % cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
             if (rc != TFFT_OK) return rc;
         }
+        tfft_set_direction(p, p->inverse, p->scale);  // hand the direction down to the sub-plans
         for (int i = 0; i < 3; ++i) {
             if (!cuda_ok(p, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking))) return TFFT_ERR_CUDA;
             if (!cuda_ok(p, cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming)) ||
@@ -548,6 +555,15 @@ int tfft_set_ft_params(tfft_plan p, double err_inj, double err_smoothing, double
     p->err_inj = err_inj;
     p->err_smoothing = err_smoothing;
     p->err_threshold = err_threshold;
+    return TFFT_OK;
+}
+
+int tfft_set_direction(tfft_plan p, int inverse, double scale) {
+    if (!p || !(scale == scale)) return TFFT_ERR_BAD_ARG;
+    p->inverse = inverse ? 1 : 0;
+    p->scale = scale;
+    if (p->chunk_plan) tfft_set_direction(p->chunk_plan, inverse, scale);
+    if (p->tail_plan) tfft_set_direction(p->tail_plan, inverse, scale);
     return TFFT_OK;
 }
 

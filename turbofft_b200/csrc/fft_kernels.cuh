@@ -60,6 +60,10 @@ struct KernelArgs {
     int inj_on;         // add err_inj to one element of one tile per selected block
     int inj_period;     // blocks b with b % inj_period == inj_phase are hit
     int inj_phase;
+    int conj_in;        // conjugate while loading (first launch of an inverse transform)
+    int scale_out;      // scale while storing (last launch): y = (y.x * scale_x, y.y * scale_y);
+    T scale_x;          // inverse transform: (s, -s) conjugates and scales; forward with a norm: (s, s)
+    T scale_y;
     T err_inj;
     T err_smoothing;
     T err_threshold;
@@ -356,6 +360,13 @@ struct Fft {
                 y[i] = cmul(y[i], w);
             }
         }
+        if (a.scale_out) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                y[i].x *= a.scale_x;
+                y[i].y *= a.scale_y;
+            }
+        }
         if constexpr (K::STAGED_IO) {
             // every thread only touches its own line here, so no barrier is needed before
 #pragma unroll
@@ -457,6 +468,10 @@ struct Fft {
         } else {
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
+        }
+        if (a.conj_in) {  // inverse transform: F^-1(x) = conj(F(conj(x))) / N
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i].y = -v[i].y;
         }
         if (DO_FT) {
             // fold(x * c) = x.x * (c.x + c.y) + x.y * (c.x - c.y); rows s + i*TPL, coalesced over s
