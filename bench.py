@@ -343,6 +343,17 @@ def run_ours(a):
             cufft.append({"logN": logn, "ms": round(ms.value, 4) if rc == 0 else None})
             tot += ms.value if rc == 0 else float("nan")
         cufft = {"gflops": flops_step / tot / 1e6, "ms_per_step": tot, "per_point": cufft}
+        # cuFFT with offline (unfused) ABFT around it: the FT-without-fusion comparison point
+        cmp.tfft_cmp_cufft_offline_abft.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                                    C.POINTER(C.c_float), C.POINTER(C.c_uint), C.c_void_p]
+        tot_ft, per_ft = 0.0, []
+        for logn in points:
+            ms, bad = C.c_float(0), C.c_uint(0)
+            rc = cmp.tfft_cmp_cufft_offline_abft(logn, 1 << (a.log_total - logn), a.datatype, x.data_ptr(), y.data_ptr(), 3,
+                                                 C.byref(ms), C.byref(bad), stream)
+            per_ft.append({"logN": logn, "ms": round(ms.value, 4) if rc == 0 else None, "failed_checks": bad.value})
+            tot_ft += ms.value if rc == 0 else float("nan")
+        cufft["offline_abft"] = {"ms_per_step": tot_ft, "overhead_vs_cufft_pct": 100 * (tot_ft / tot - 1), "per_point": per_ft}
 
     # ---- end to end through the public host-buffer API (tfft_exec_host)
     e2e = None
