@@ -335,14 +335,39 @@ def run_ours(a):
         cmp = C.CDLL(os.path.join(os.path.dirname(tf.__file__), "libturbofft_cufft_cmp.so"))
         cmp.tfft_cmp_cufft.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                        C.POINTER(C.c_float), C.c_void_p]
-        cufft, tot = [], 0.0
+        cmp.tfft_cmp_cufft_plan_create.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.POINTER(C.c_int)]
+        cmp.tfft_cmp_cufft_plan_exec.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        handles = {}
         for logn in points:
-            ms = C.c_float(0)
-            rc = cmp.tfft_cmp_cufft(logn, 1 << (a.log_total - logn), a.datatype, x.data_ptr(), y.data_ptr(), 5,
-                                    C.byref(ms), stream)
-            cufft.append({"logN": logn, "ms": round(ms.value, 4) if rc == 0 else None})
-            tot += ms.value if rc == 0 else float("nan")
-        cufft = {"gflops": flops_step / tot / 1e6, "ms_per_step": tot, "per_point": cufft}
+            h = C.c_int(0)
+            if cmp.tfft_cmp_cufft_plan_create(logn, 1 << (a.log_total - logn), a.datatype, stream, C.byref(h)) == 0:
+                handles[logn] = h.value
+
+        def cufft_step(events=None):
+            for i, logn in enumerate(points):
+                if logn in handles:
+                    cmp.tfft_cmp_cufft_plan_exec(handles[logn], a.datatype, x.data_ptr(), y.data_ptr())
+                if events is not None:
+                    events[i + 1].record()
+
+        # same protocol as ours: warm-up sweeps, then K sweeps back to back with per-point events
+        for _ in range(max(a.warmup, 3)):
+            cufft_step()
+        torch.cuda.synchronize()
+        cev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(points) + 1)] for _ in range(a.steps)]
+        for k in range(a.steps):
+            cev[k][0].record()
+            cufft_step(cev[k])
+        torch.cuda.synchronize()
+        cufft, tot = [], 0.0
+        for i, logn in enumerate(points):
+            ms = sum(ev[i].elapsed_time(ev[i + 1]) for ev in cev) / a.steps
+            cufft.append({"logN": logn, "ms": round(ms, 4) if logn in handles else None})
+            tot += ms if logn in handles else float("nan")
+        for h in handles.values():
+            cmp.tfft_cmp_cufft_plan_destroy(h)
+        cufft = {"gflops": flops_step / tot / 1e6, "ms_per_step": tot, "per_point": cufft,
+                 "protocol": "same as ours: warm-up sweeps, then %d sweeps back to back" % a.steps}
         # cuFFT with offline (unfused) ABFT around it: the FT-without-fusion comparison point
         cmp.tfft_cmp_cufft_offline_abft.argtypes = [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                                     C.POINTER(C.c_float), C.POINTER(C.c_uint), C.c_void_p]

@@ -81,3 +81,54 @@ def test_config4_ft_full_size(torch_cuda):
         # detect-only run on clean data: silent
         p1 = tf.Plan(logn, batch, 0, if_ft=1, thread_bs=tbs)
         assert torch.equal(p1(x), clean) and p1.ft_status()[0] == 0
+
+
+def _chunked_energy(torch, t, chunk=1 << 26):
+    flat = t.view(-1)
+    tot = 0.0
+    for i in range(0, flat.numel(), chunk):
+        c = flat[i:i + chunk]
+        tot += float((c.real.double() ** 2 + c.imag.double() ** 2).sum())
+    return tot
+
+
+@pytest.mark.parametrize("dtype,logn", [(0, 26), (0, 28), (0, 30), (1, 27)])
+def test_single_long_transform_on_one_gpu(torch_cuda, dtype, logn):
+    """Three-launch plans far beyond the reference's table (which stops at 2^25 and overflows
+    32-bit indices at 2^31 elements): 64-bit indexing, checked by Parseval, by the analytic
+    transform of impulse + tone, and for 2^26 against the float64 oracle."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    n = 1 << logn
+    cd = np.complex64 if dtype == 0 else np.complex128
+    tol = orc.tolerance(cd, logn)
+    x = _make(torch, dtype, n, seed=logn)
+    plan = tf.Plan(logn, 1, dtype)
+    y = plan(x)
+    torch.cuda.synchronize()
+    assert abs(_chunked_energy(torch, y) / (n * _chunked_energy(torch, x)) - 1.0) <= 10 * tol
+    if logn <= 26:
+        ref = orc.fft_forward(x.cpu().numpy())
+        assert orc.rel_l2(y.cpu().numpy(), ref) <= tol
+        del ref
+    del y
+    # impulse at n0 plus a pure tone at k0: X[k] = exp(-2 pi i n0 k / N) + N [k == k0]
+    n0, k0 = 12345, 54321
+    x.zero_()
+    step = 1 << 24
+    for i in range(0, n, step):
+        j = torch.arange(i, i + step, device="cuda", dtype=torch.int64)
+        ph = ((j * k0) % n).double() * (2 * np.pi / n)
+        x[i:i + step] = torch.polar(torch.full_like(ph, 1.0 / n), ph).to(x.dtype)
+    x[n0] += 1.0
+    y = plan(x)
+    worst = 0.0
+    for i in range(0, n, step):
+        k = torch.arange(i, i + step, device="cuda", dtype=torch.int64)
+        ph = ((k * n0) % n).double() * (-2 * np.pi / n)
+        want = torch.polar(torch.ones_like(ph), ph)
+        if i <= k0 < i + step:
+            want[k0 - i] += 1.0
+        worst = max(worst, float((y[i:i + step].to(torch.complex128) - want).abs().max()))
+    assert worst <= 50 * tol, worst

@@ -49,6 +49,30 @@ int tfft_cmp_cufft(int logN, long long batch, int dtype, const void* in, void* o
     return ce == cudaSuccess ? 0 : -(int)ce;
 }
 
+// Plan once, execute many times: lets the benchmark run a whole cuFFT sweep back to back the
+// same way it runs ours (same thermal and power state).
+int tfft_cmp_cufft_plan_create(int logN, long long batch, int dtype, void* stream, int* handle_out) {
+    cufftHandle plan;
+    if (!handle_out || cufftCreate(&plan) != CUFFT_SUCCESS) return -1;
+    long long n[1] = {1LL << logN};
+    size_t work = 0;
+    cufftResult r = cufftMakePlanMany64(plan, 1, n, nullptr, 1, 1LL << logN, nullptr, 1, 1LL << logN,
+                                        dtype == 0 ? CUFFT_C2C : CUFFT_Z2Z, batch, &work);
+    if (r != CUFFT_SUCCESS) {
+        cufftDestroy(plan);
+        return -(int)r - 100;
+    }
+    cufftSetStream(plan, (cudaStream_t)stream);
+    *handle_out = (int)plan;
+    return 0;
+}
+int tfft_cmp_cufft_plan_exec(int handle, int dtype, const void* in, void* out) {
+    const cufftResult r = dtype == 0 ? cufftExecC2C((cufftHandle)handle, (cufftComplex*)in, (cufftComplex*)out, CUFFT_FORWARD)
+                                     : cufftExecZ2Z((cufftHandle)handle, (cufftDoubleComplex*)in, (cufftDoubleComplex*)out, CUFFT_FORWARD);
+    return r == CUFFT_SUCCESS ? 0 : -(int)r - 100;
+}
+int tfft_cmp_cufft_plan_destroy(int handle) { return cufftDestroy((cufftHandle)handle) == CUFFT_SUCCESS ? 0 : -1; }
+
 // "Offline" ABFT around cuFFT, the shape of the reference's unused prototype
 // (include/cufft/cufft_ft.h:19-156 with include/cufft/reduction.cuh:1-27): per-position sums
 // over groups of 16 signals are appended to the batch, cuFFT transforms batch + batch/16
@@ -60,9 +84,11 @@ namespace {
 
 template <typename C>
 __global__ void __launch_bounds__(256) group_sum_kernel(const C* __restrict__ a, C* __restrict__ sums, long long n, int m) {
-    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long chunks = (n + 255) / 256;
+    const long long grp = blockIdx.x / chunks;
+    const long long i = (blockIdx.x % chunks) * 256 + threadIdx.x;
     if (i >= n) return;
-    const C* p = a + (long long)blockIdx.y * m * n + i;
+    const C* p = a + grp * m * n + i;
     C acc;
     acc.x = acc.y = 0;
     for (int k = 0; k < m; ++k) {
@@ -70,15 +96,17 @@ __global__ void __launch_bounds__(256) group_sum_kernel(const C* __restrict__ a,
         acc.x += v.x;
         acc.y += v.y;
     }
-    sums[(long long)blockIdx.y * n + i] = acc;
+    sums[grp * n + i] = acc;
 }
 
 template <typename C>
 __global__ void __launch_bounds__(256) group_check_kernel(const C* __restrict__ y, const C* __restrict__ want, long long n, int m,
                                                           double tol, unsigned int* bad) {
-    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long chunks = (n + 255) / 256;
+    const long long grp = blockIdx.x / chunks;
+    const long long i = (blockIdx.x % chunks) * 256 + threadIdx.x;
     if (i >= n) return;
-    const C* p = y + (long long)blockIdx.y * m * n + i;
+    const C* p = y + grp * m * n + i;
     double sx = 0, sy = 0, mag = 0;
     for (int k = 0; k < m; ++k) {
         const C v = p[(long long)k * n];
@@ -86,7 +114,7 @@ __global__ void __launch_bounds__(256) group_check_kernel(const C* __restrict__ 
         sy += v.y;
         mag += fabs((double)v.x) + fabs((double)v.y);
     }
-    const C w = want[(long long)blockIdx.y * n + i];
+    const C w = want[grp * n + i];
     if (fabs(sx - w.x) + fabs(sy - w.y) > tol * (1.0 + mag)) atomicAdd(bad, 1u);
 }
 
@@ -127,15 +155,15 @@ int tfft_cmp_cufft_offline_abft(int logN, long long batch, int dtype, const void
             cudaMemsetAsync(bad, 0, sizeof(unsigned int), st);
             // sums of the inputs, their transform (the expected sums of the outputs), the batch, the check
             if (dtype == 0) {
-                group_sum_kernel<cufftComplex><<<dim3((unsigned)((n + 255) / 256), (unsigned)groups), 256, 0, st>>>((const cufftComplex*)in, (cufftComplex*)sums_in, n, 16);
+                group_sum_kernel<cufftComplex><<<dim3((unsigned)(((n + 255) / 256) * groups)), 256, 0, st>>>((const cufftComplex*)in, (cufftComplex*)sums_in, n, 16);
                 if (cufftExecC2C(plan_sums, (cufftComplex*)sums_in, (cufftComplex*)sums_out, CUFFT_FORWARD) != CUFFT_SUCCESS) rc = -5;
                 if (!rc && cufftExecC2C(plan, (cufftComplex*)in, (cufftComplex*)out, CUFFT_FORWARD) != CUFFT_SUCCESS) rc = -5;
-                group_check_kernel<cufftComplex><<<dim3((unsigned)((n + 255) / 256), (unsigned)groups), 256, 0, st>>>((const cufftComplex*)out, (const cufftComplex*)sums_out, n, 16, 1e-4, bad);
+                group_check_kernel<cufftComplex><<<dim3((unsigned)(((n + 255) / 256) * groups)), 256, 0, st>>>((const cufftComplex*)out, (const cufftComplex*)sums_out, n, 16, 1e-4, bad);
             } else {
-                group_sum_kernel<cufftDoubleComplex><<<dim3((unsigned)((n + 255) / 256), (unsigned)groups), 256, 0, st>>>((const cufftDoubleComplex*)in, (cufftDoubleComplex*)sums_in, n, 16);
+                group_sum_kernel<cufftDoubleComplex><<<dim3((unsigned)(((n + 255) / 256) * groups)), 256, 0, st>>>((const cufftDoubleComplex*)in, (cufftDoubleComplex*)sums_in, n, 16);
                 if (cufftExecZ2Z(plan_sums, (cufftDoubleComplex*)sums_in, (cufftDoubleComplex*)sums_out, CUFFT_FORWARD) != CUFFT_SUCCESS) rc = -5;
                 if (!rc && cufftExecZ2Z(plan, (cufftDoubleComplex*)in, (cufftDoubleComplex*)out, CUFFT_FORWARD) != CUFFT_SUCCESS) rc = -5;
-                group_check_kernel<cufftDoubleComplex><<<dim3((unsigned)((n + 255) / 256), (unsigned)groups), 256, 0, st>>>((const cufftDoubleComplex*)out, (const cufftDoubleComplex*)sums_out, n, 16, 1e-11, bad);
+                group_check_kernel<cufftDoubleComplex><<<dim3((unsigned)(((n + 255) / 256) * groups)), 256, 0, st>>>((const cufftDoubleComplex*)out, (const cufftDoubleComplex*)sums_out, n, 16, 1e-11, bad);
             }
         }
         cudaEventRecord(e1, st);
