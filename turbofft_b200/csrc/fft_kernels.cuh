@@ -29,6 +29,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#ifndef TFFT_FT_OCC
+#define TFFT_FT_OCC 3  // quarters of the plain kernels' resident-thread target that the FT variants aim for
+#endif
+
 namespace tfft {
 
 enum { ROLE_SINGLE = 0, ROLE_FIRST = 1, ROLE_LAST = 2 };
@@ -212,7 +216,7 @@ struct Cfg {
     // The FT variants carry the checksum state on top and get a quarter more registers.
     static constexpr int SMEM_BLOCKS = SMEM_BYTES ? (int)((220 * 1024) / SMEM_BYTES) : 32;
     static constexpr int min_blocks(bool ft) {
-        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? 3 : 4) / 4;
+        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? TFFT_FT_OCC : 4) / 4;
         const int tb = (target + THREADS - 1) / THREADS;
         const int b = SMEM_BLOCKS < tb ? SMEM_BLOCKS : tb;
         return b < 1 ? 1 : b;

@@ -132,7 +132,7 @@ def cmd_run(a):
                 os.unlink(path)
                 continue
             os.unlink(path)
-            for _ in range(2):
+            for _ in range(a.burn):   # --burn > 2 brings the GPU to its sustained, power-capped clocks first
                 plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -185,6 +185,7 @@ def main(argv=None):
         if name == "run":
             p.add_argument("--log-total", type=int, default=28)
             p.add_argument("--reps", type=int, default=5)
+            p.add_argument("--burn", type=int, default=2, help="untimed runs before the timed ones")
             p.add_argument("--out", default="tune_results.json")
         if name == "apply":
             p.add_argument("--results", required=True)
