@@ -123,3 +123,48 @@ def test_product_never_imports_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"(import\s+oracle|from\s+oracle|oracle/)", text), os.path.join(dirpath, f)
+
+
+def test_tuner_candidates_are_plannable():
+    """Every row the tuner proposes must pass the planner's checks (so that a compiled
+    candidate can never be launched with an impossible geometry)."""
+    from turbofft_b200 import tune
+
+    for dt in ("float2", "double2"):
+        for logn in (3, 9, 13, 16, 21, 24):
+            cands = tune.candidates(logn, dt)
+            assert cands, (dt, logn)
+            for r in cands:
+                planner.validate_row(r)
+                for l in planner.launches_of_row(r):
+                    assert 32 <= l.threads <= 1024
+                    assert l.role != planner.ROLE_LAST or l.stages >= 2
+                assert tune.row_text(r).count(",") == 10
+
+
+def test_shipped_shared_memory_layouts_are_conflict_free():
+    """The generator's bank model on a few shipped instances: the chosen (PADSHIFT, EXTRA)
+    reaches the ideal wavefront count, the unpadded layout does not."""
+    from turbofft_b200.codegen import smem_layout as sl
+
+    cache = sl.load_cache()
+    for key in ("0_0_12_4_0", "0_1_8_4_4", "0_2_8_4_4", "1_0_12_4_0"):
+        assert key in cache, key
+        f64, role, logm, loge, logc = (int(t) for t in key.split("_"))
+        ps, ex = cache[key]
+        tot, ideal, _ = sl.simulate(role, logm, loge, logc, bool(f64), ps, ex)
+        assert tot == ideal, (key, tot, ideal)
+    tot, ideal, _ = sl.simulate(0, 12, 4, 0, False, sl.NO_PAD, 0)
+    assert tot > ideal
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    import json
+
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          "--cpu-log-sample", "18", "--lo", "7", "--hi", "12"], capture_output=True, text=True, check=True).stdout
+    lines = [l for l in out.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["unit"] == "GFLOPS" and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["e2e"]["h2d_bytes_per_step"] == 0
