@@ -84,6 +84,17 @@ int tfft_plan_info(tfft_plan plan, int* info);
  * as run-time values.  Defaults: 100, 1000, 1e-3. */
 int tfft_set_ft_params(tfft_plan plan, double err_inj, double err_smoothing, double err_threshold);
 
+/* How a located tile is repaired (plans created with if_err).  0 (default): recompute it
+ * from its input, what the reference's generated kernels do (fft_codegen.py:149-193).
+ * 1: subtract sum(y) - F(sum(x)) taken over the block's tiles, the correction the reference
+ * prepares (it accumulates both sums, fft_codegen.py:356-357,422-423) but leaves commented
+ * out (:370,:403,:427-429; test.ipynb cell 0).  It does not read the input again, so a
+ * 1-launch plan may then run in place; it costs two more tiles of shared memory per block.
+ * Available for single and last launches (first/middle launches keep recomputing, their
+ * input is never overwritten); TFFT_ERR_UNSUPPORTED if no launch of the plan has it.
+ * The repaired outputs equal the fault-free ones up to rounding, not bit for bit. */
+int tfft_set_correction(tfft_plan plan, int from_checksums);
+
 /* Direction and normalisation (no counterpart in the reference, which is forward and
  * unnormalised only).  inverse != 0 computes scale * conj(F(conj(x))), i.e. the inverse DFT
  * for scale = 1/N; inverse == 0 computes scale * F(x).  The conjugations and the scaling

@@ -187,6 +187,33 @@ def test_decisions_match_cpu_model(torch_cuda, logn, tbs, dtype):
         assert abs(gw - d["delta_w"]) <= rt * (abs(d["delta_w"]) + 1e-3 * d["S"] * tbs + 1)
 
 
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("logn,batch,tbs,inplace", [(7, 512, 4, True), (10, 64, 2, True), (10, 64, 8, False), (12, 64, 4, True),
+                                                   (16, 16, 4, False), (18, 8, 2, True)])
+def test_correction_from_checksums(torch_cuda, logn, batch, tbs, inplace, dtype):
+    """tfft_set_correction(1): the located tile is repaired with sum(y) - F(sum(x)) over the
+    block's tiles (the reference's commented-out path, fft_codegen.py:356-357,422-429) instead
+    of being recomputed, so single-launch plans may run in place.  Same detections and located
+    indices as the recompute mode; repaired values agree with the fault-free run to rounding."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    x = (orc.make_input(batch, 1 << logn, CD[dtype], seed=logn + 7) * 0.01).astype(CD[dtype])
+    _, y0 = _run(torch, logn, batch, dtype, x)
+    ref = tf.Plan(logn, batch, dtype, if_ft=1, if_err=1, thread_bs=tbs)
+    ref(torch.from_numpy(x).cuda())
+    nd0, nc0, loc0 = ref.ft_status()
+    plan = tf.Plan(logn, batch, dtype, if_ft=1, if_err=1, thread_bs=tbs)
+    plan.set_correction(True)
+    xd = torch.from_numpy(x).cuda()
+    y = plan(xd, out=xd if inplace else None).cpu().numpy()
+    nd, nc, loc = plan.ft_status()
+    assert (nd, nc, loc) == (nd0, nc0, loc0) and nd == len(loc) > 0
+    scale = np.abs(y0).max()
+    assert np.abs(y - y0).max() <= (2e-5 if dtype == 0 else 1e-12) * scale * tbs
+    assert orc.rel_l2(y, orc.fft_forward(x)) <= 4 * orc.tolerance(CD[dtype], logn)
+
+
 def test_threshold_parameters_are_honoured(torch_cuda):
     """A tiny fault stays below err_threshold and is ignored; lowering the threshold finds it."""
     import turbofft_b200 as tf

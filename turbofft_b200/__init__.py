@@ -95,6 +95,10 @@ class Plan:
     def workspace_bytes(self) -> int:
         return int(lib().tfft_workspace_bytes(self._h))
 
+    def set_correction(self, from_checksums: bool = True):
+        """Repair located tiles from the running checksums (no recompute; allows 1-launch in place)."""
+        _lib.check(lib().tfft_set_correction(self._h, int(from_checksums)), "tfft_set_correction", self._h)
+
     def set_direction(self, inverse: bool = False, scale: float = 1.0):
         """inverse: scale * conj(F(conj(x))) (the inverse DFT for scale = 1/N); else scale * F(x)."""
         _lib.check(lib().tfft_set_direction(self._h, int(inverse), float(scale)), "tfft_set_direction")

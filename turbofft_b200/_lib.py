@@ -26,6 +26,7 @@ SIGNATURES = {
     "tfft_workspace_bytes": (C.c_size_t, [C.c_void_p]),
     "tfft_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "tfft_set_ft_params": (C.c_int, [C.c_void_p, C.c_double, C.c_double, C.c_double]),
+    "tfft_set_correction": (C.c_int, [C.c_void_p, C.c_int]),
     "tfft_set_direction": (C.c_int, [C.c_void_p, C.c_int, C.c_double]),
     "tfft_set_injection": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tfft_ft_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int),

@@ -44,7 +44,8 @@ def nvcc() -> str:
 def run_codegen(verbose: bool = True) -> None:
     gen = os.path.join(PKG, "codegen", "fft_codegen.py")
     for dt in ("float2", "double2"):
-        for extra in ([], ["--if_ft", "1"], ["--if_ft", "1", "--if_err_injection", "1"]):
+        for extra in ([], ["--if_ft", "1"], ["--if_ft", "1", "--if_err_injection", "1"],
+                      ["--if_ft", "1", "--if_err_injection", "2"]):
             cmd = [sys.executable, gen, "--gpu", "B200", "--datatype", dt] + extra
             res = subprocess.run(cmd, capture_output=True, text=True)
             if res.returncode != 0:

@@ -88,6 +88,7 @@ struct tfft_plan_s {
     double err_threshold = TFFT_DEFAULT_ERR_THRESHOLD;
     int inj_enable = 0, inj_launch = -1, inj_period = 1, inj_phase = 0;
     int diag = 0;
+    int csum = 0;        // 1: repair from the running checksums (FT_CSUM kernels) where they exist
     int inverse = 0;     // 0: forward; 1: conjugate in, conjugate out (inverse transform)
     double scale = 1.0;  // applied with the conjugation of the last launch
     cudaStream_t last_stream = nullptr;
@@ -254,6 +255,9 @@ int ilog2_exact(long long x) {
     return ((1LL << l) == x) ? l : -1;
 }
 
+// a launch can repair from the running checksums if the kernel exists and its three tiles fit
+bool csum_ok(const KernelEntry* k) { return k && k->fn[FT_CSUM] && k->smem_csum <= 227u * 1024u; }
+
 template <typename T>
 int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
     typedef typename Cplx<T>::type C;
@@ -294,8 +298,10 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         a.ft_count = p->ft_count ? p->ft_count + 2 * i : nullptr;
         a.ft_diag = p->diag ? (T*)d.ft_diag : nullptr;
         void* args[] = {&a};
-        const void* fn = d.k->fn[ftmode];
-        if (!cuda_ok(p, cudaLaunchKernel(fn, dim3(d.grid), dim3(d.k->threads), args, d.k->smem, st)))
+        const bool use_csum = ftmode == FT_CORRECT && p->csum && csum_ok(d.k);
+        const void* fn = use_csum ? d.k->fn[FT_CSUM] : d.k->fn[ftmode];
+        const size_t smem = use_csum ? d.k->smem_csum : d.k->smem;
+        if (!cuda_ok(p, cudaLaunchKernel(fn, dim3(d.grid), dim3(d.k->threads), args, smem, st)))
             return TFFT_ERR_CUDA;
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
@@ -412,7 +418,7 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
 
 int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
     if (!p || !in || !out) return TFFT_ERR_BAD_ARG;
-    if (in == out && p->n_launch == 1 && p->if_err) return TFFT_ERR_UNSUPPORTED;
+    if (in == out && p->n_launch == 1 && p->if_err && !(p->csum && csum_ok(p->L[0].k))) return TFFT_ERR_UNSUPPORTED;
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
@@ -555,6 +561,27 @@ int tfft_set_ft_params(tfft_plan p, double err_inj, double err_smoothing, double
     p->err_inj = err_inj;
     p->err_smoothing = err_smoothing;
     p->err_threshold = err_threshold;
+    return TFFT_OK;
+}
+
+int tfft_set_correction(tfft_plan p, int from_checksums) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    if (from_checksums && !p->if_err) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (from_checksums) {
+        bool any = false;
+        for (int i = 0; i < p->n_launch; ++i) {
+            const KernelEntry* k = p->L[i].k;
+            if (!csum_ok(k)) continue;  // this launch keeps recomputing
+            any = true;
+            if (k->smem_csum > 40 * 1024 &&
+                !cuda_ok(p, cudaFuncSetAttribute(k->fn[FT_CSUM], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem_csum)))
+                return TFFT_ERR_CUDA;
+        }
+        if (!any) return TFFT_ERR_UNSUPPORTED;
+    }
+    p->csum = from_checksums ? 1 : 0;
     return TFFT_OK;
 }
 

@@ -26,6 +26,11 @@
 // left side  sum_p fold(x_p * c_p) with c = W_M r taken while loading,
 // right side sum_k fold(y_k * r_{k mod 3}) taken before the store,
 // and a copy weighted by the 1-based tile counter that locates the tile.
+// FT_CORRECT repairs the located tile by recomputing it from its input (what the reference
+// ships, fft_codegen.py:149-193); FT_CSUM repairs it from the per-position sums of the
+// block's inputs and outputs, y_bad -= sum(y) - F(sum(x)) -- the correction the reference
+// accumulates rPtr_3 / rPtr_4 for but leaves commented out (fft_codegen.py:356-357,
+// 422-429; test.ipynb cell 0) -- which does not need the input again.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -36,7 +41,7 @@
 namespace tfft {
 
 enum { ROLE_SINGLE = 0, ROLE_FIRST = 1, ROLE_LAST = 2 };
-enum { FT_OFF = 0, FT_DETECT = 1, FT_CORRECT = 2 };
+enum { FT_OFF = 0, FT_DETECT = 1, FT_CORRECT = 2, FT_CSUM = 3 };
 
 template <typename T> struct Cplx;
 template <> struct Cplx<float> { typedef float2 type; };
@@ -211,6 +216,8 @@ struct Cfg {
     static constexpr bool STAGED_IO = (ROLE == ROLE_SINGLE && S == 1 && TPL == 1 && LOGM >= 2);
     static constexpr int SMEM_ELEMS = STAGED_IO ? (M + 1) * C : (S > 1 ? (LAYOUT_COLS ? MPAD * C : PITCH * C) : 0);
     static constexpr size_t SMEM_BYTES = (size_t)SMEM_ELEMS * 2 * sizeof(T);
+    // FT_CSUM keeps two more tiles in shared memory: the running sums of inputs and outputs
+    static constexpr size_t smem_bytes(int ft) { return SMEM_BYTES + (ft == FT_CSUM ? (size_t)2 * M * C * 2 * sizeof(T) : 0); }
     // Occupancy target handed to the compiler as the register cap: enough blocks for
     // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
     // The FT variants carry the checksum state on top and get a quarter more registers.
@@ -315,7 +322,9 @@ struct Fft {
     }
 
     // Final stage: natural-order outputs, right checksum, inter-launch twiddle, store.
-    template <int LR, bool DO_FT>
+    // CS: 0 plain, 1 add the outputs to the block's running sum, 2 correction pass (v holds
+    // F(sum of inputs); the located tile's stored outputs get sum(y) - F(sum(x)) subtracted)
+    template <int LR, bool DO_FT, int CS>
     static __device__ __forceinline__ void finish(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g, int s, int c,
                                                   const FtRegs& f, T& tout) {
         constexpr int R = 1 << LR, NB = E / R;
@@ -331,6 +340,15 @@ struct Fft {
                 const int cls = (i * t3) % 3;
                 tout = fma(y[i].x, f.al[cls], tout);
                 tout = fma(y[i].y, f.be[cls], tout);
+            }
+        }
+        if constexpr (CS != 0) {
+            C* sy = sm + K::SMEM_ELEMS + E * K::THREADS + threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                const C acc = sy[i * K::THREADS];
+                if (CS == 1) sy[i * K::THREADS] = cadd(acc, y[i]);
+                else y[i] = csub(acc, y[i]);  // the error this block's outputs carry at this position
             }
         }
         if (ROLE == ROLE_FIRST) {
@@ -386,11 +404,14 @@ struct Fft {
         } else if (c < g.ncols) {
             C* dst = a.out + g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
 #pragma unroll
-            for (int i = 0; i < E; ++i) dst[(long long)i * TPL * g.out_rs] = y[i];
+            for (int i = 0; i < E; ++i) {
+                if (CS == 2) dst[(long long)i * TPL * g.out_rs] = csub(dst[(long long)i * TPL * g.out_rs], y[i]);
+                else dst[(long long)i * TPL * g.out_rs] = y[i];
+            }
         }
     }
 
-    template <int ST, bool DO_FT>
+    template <int ST, bool DO_FT, int CS>
     static __device__ __forceinline__ void stage(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g,
                                                  const FtRegs& f, T& tout) {
         constexpr int LR = logR<ST>(), R = 1 << LR, LP = logP<ST>(), P = 1 << LP, NB = E / R;
@@ -434,22 +455,28 @@ struct Fft {
                 }
             }
             __syncthreads();
-            stage<ST + 1, DO_FT>(v, sm, a, g, f, tout);
+            stage<ST + 1, DO_FT, CS>(v, sm, a, g, f, tout);
         } else {
-            finish<LR, DO_FT>(v, sm, a, g, s, c, f, tout);
+            finish<LR, DO_FT, CS>(v, sm, a, g, s, c, f, tout);
         }
     }
 
     // One tile: load, all stages, store.  tin/tout receive this thread's share of the
     // tile's left and right checksums.
-    template <bool DO_FT, bool DO_INJ>
+    template <bool DO_FT, bool DO_INJ, int CS = 0>
     static __device__ __forceinline__ void tile(const KernelArgs<T>& a, C* sm, long long tile_id, bool inject,
                                                 const FtRegs& f, T& tin, T& tout) {
+        static_assert(CS == 0 || (!K::STAGED_IO && ROLE != ROLE_FIRST), "checksum correction: single and last launches only");
         const Geom g = decode(a, tile_id);
         int s, c;
         map_thread<K::CFAST_IN>(s, c);
         C v[E];
-        if constexpr (K::STAGED_IO) {
+        if constexpr (CS == 2) {
+            // the "signal" of the correction pass is the sum of the block's inputs
+            const C* sx = sm + K::SMEM_ELEMS + threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = sx[i * K::THREADS];
+        } else if constexpr (K::STAGED_IO) {
             // flat element f of the tile = line f / M, row f % M; consecutive threads, consecutive f
             const long long valid = (long long)g.ncols << LOGM;
             const C* src = a.in + g.in_base;
@@ -473,9 +500,14 @@ struct Fft {
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
         }
-        if (a.conj_in) {  // inverse transform: F^-1(x) = conj(F(conj(x))) / N
+        if (CS != 2 && a.conj_in) {  // inverse transform: F^-1(x) = conj(F(conj(x))) / N
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].y = -v[i].y;
+        }
+        if constexpr (CS == 1) {  // before the fault is injected, as the reference sums rPtr_3
+            C* sx = sm + K::SMEM_ELEMS + threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < E; ++i) sx[i * K::THREADS] = cadd(sx[i * K::THREADS], v[i]);
         }
         if (DO_FT) {
             // fold(x * c) = x.x * (c.x + c.y) + x.y * (c.x - c.y); rows s + i*TPL, coalesced over s
@@ -490,7 +522,7 @@ struct Fft {
         if (DO_INJ) {
             if (inject && threadIdx.x == 0) v[0].x += a.err_inj;
         }
-        stage<0, DO_FT>(v, sm, a, g, f, tout);
+        stage<0, DO_FT, CS>(v, sm, a, g, f, tout);
     }
 
     static __device__ __forceinline__ T warp_sum(T x) {
@@ -533,11 +565,18 @@ struct Fft {
         const int inj_it = (int)((blockIdx.x / (unsigned)a.inj_period) % (unsigned)a.tiles_per_cta);
         T acc_in = 0, acc_out = 0, acc_w = 0;
         int done = 0;
+        constexpr int CSACC = (FT == FT_CSUM) ? 1 : 0;
+        if constexpr (FT == FT_CSUM) {
+            // running sums live in shared memory, one slot per (thread, register): nobody else touches them
+            C* sums = sm + K::SMEM_ELEMS + threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < 2 * E; ++i) sums[i * K::THREADS].x = sums[i * K::THREADS].y = T(0);
+        }
         for (int it = 0; it < a.tiles_per_cta; ++it) {
             const long long t = blockIdx.x + it * grid;
             if (t >= a.n_tiles) break;
             T tin = 0, tout = 0;
-            tile<true, true>(a, sm, t, hit && it == inj_it, f, tin, tout);
+            tile<true, true, CSACC>(a, sm, t, hit && it == inj_it, f, tin, tout);
             acc_in += tin;
             acc_out += tout;
             acc_w = fma(T(it + 1), tin - tout, acc_w);
@@ -578,12 +617,21 @@ struct Fft {
             }
         }
         __syncthreads();
-        if (FT == FT_CORRECT) {
+        if constexpr (FT == FT_CORRECT) {
             // recompute the located tile from the untouched input (fft_codegen.py:149-193)
             const int k = s_k;
             if (k >= 1 && k <= done) {
                 T tin = 0, tout = 0;
                 tile<false, false>(a, sm, blockIdx.x + (long long)(k - 1) * grid, false, f, tin, tout);
+                if (threadIdx.x == 0) atomicAdd(a.ft_count + 1, 1u);
+            }
+        }
+        if constexpr (FT == FT_CSUM) {
+            // transform the summed inputs and take sum(y) - F(sum(x)) off the located tile's outputs
+            const int k = s_k;
+            if (k >= 1 && k <= done) {
+                T tin = 0, tout = 0;
+                tile<false, false, 2>(a, sm, blockIdx.x + (long long)(k - 1) * grid, false, f, tin, tout);
                 if (threadIdx.x == 0) atomicAdd(a.ft_count + 1, 1u);
             }
         }

@@ -7,7 +7,8 @@
 #define TFFT_CAT2(a, b) a##b
 #define TFFT_CAT(a, b) TFFT_CAT2(a, b)
 
-// T: float|double, DT: 0|1, ROLE: 0 single, 1 first/middle, 2 last, FT: 0 off, 1 detect, 2 correct
+// T: float|double, DT: 0|1, ROLE: 0 single, 1 first/middle, 2 last, FT: 0 off, 1 detect, 2 correct (recompute),
+// 3 correct from the running checksums (single and last launches only)
 #define TFFT_INST(T, DT, LOGM, LOGE, LOGC, ROLE, FT)                                                        \
     template __global__ void tfft::fft_kernel<T, LOGM, LOGE, LOGC, ROLE, FT>(                               \
         const __grid_constant__ tfft::KernelArgs<T>);                                                       \
@@ -17,7 +18,7 @@
             typedef tfft::Cfg<T, LOGM, LOGE, LOGC, ROLE> K;                                                 \
             tfft::register_kernel(DT, ROLE, LOGM, LOGE, LOGC, FT,                                           \
                                   (const void*)&tfft::fft_kernel<T, LOGM, LOGE, LOGC, ROLE, FT>, K::THREADS, \
-                                  K::SMEM_BYTES);                                                           \
+                                  K::smem_bytes(FT));                                                           \
         }                                                                                                   \
     } TFFT_CAT(tfft_reg_, __LINE__);                                                                        \
     }

@@ -17,7 +17,8 @@ void register_kernel(int dtype, int role, int logm, int loge, int logc, int ft, 
     KernelEntry& e = table()[Key(dtype, role, logm, loge, logc)];
     e.fn[ft] = fn;
     e.threads = threads;
-    e.smem = smem;
+    if (ft == 3) e.smem_csum = smem;
+    else e.smem = smem;
 }
 
 const KernelEntry* find_kernel(int dtype, int role, int logm, int loge, int logc) {
@@ -28,7 +29,7 @@ const KernelEntry* find_kernel(int dtype, int role, int logm, int loge, int logc
 int registered_kernel_count() {
     int n = 0;
     for (auto& kv : table())
-        for (int f = 0; f < 3; ++f) n += kv.second.fn[f] != nullptr;
+        for (int f = 0; f < 4; ++f) n += kv.second.fn[f] != nullptr;
     return n;
 }
 

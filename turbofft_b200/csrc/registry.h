@@ -9,9 +9,10 @@
 namespace tfft {
 
 struct KernelEntry {
-    const void* fn[3];  // FT_OFF, FT_DETECT, FT_CORRECT (null = not compiled)
+    const void* fn[4];  // FT_OFF, FT_DETECT, FT_CORRECT, FT_CSUM (null = not compiled)
     int threads;
-    size_t smem;
+    size_t smem;        // dynamic shared memory of the first three modes
+    size_t smem_csum;   // FT_CSUM adds two tiles of running sums
 };
 
 void register_kernel(int dtype, int role, int logm, int loge, int logc, int ft, const void* fn, int threads,
