@@ -158,7 +158,7 @@ def test_fused_four_step_single_gpu(torch_cuda, dtype, logn, natural):
     torch = torch_cuda
     npdt = np.complex64 if dtype == 0 else np.complex128
     x = orc.make_input(1, 1 << logn, npdt, seed=logn)[0]
-    fs = mg.FusedFourStepFFT(logn, 1, 0, dtype, 0, natural_order=natural, if_ft=1)
+    fs = mg.FusedFourStepFFT(logn, 1, 0, dtype, 0, natural_order=natural, if_ft=1, pipeline=2 if logn >= 16 else 1)
     y = fs(torch.from_numpy(x).cuda()).cpu().numpy()
     y2 = fs(torch.from_numpy(x).cuda()).cpu().numpy()     # buffers reused by a second call
     fs.close()
@@ -193,7 +193,14 @@ def _gpu_worker(rank, world, port, logn, dtype, q):
         torch.cuda.synchronize()
         dist.barrier()
         fused.close()
-        q.put((rank, max(orc.rel_l2(y, ref), orc.rel_l2(yf, ref), orc.rel_l2(yf2, ref))))
+        # and with each exchange cut into pieces that overlap the local transforms
+        piped = mg.FusedFourStepFFT(logn, world, rank, dtype, rank, natural_order=True, if_ft=1, pipeline=2)
+        yp = piped(xg).cpu().numpy()
+        yp2 = piped(xg).cpu().numpy()
+        torch.cuda.synchronize()
+        dist.barrier()
+        piped.close()
+        q.put((rank, max(orc.rel_l2(y, ref), orc.rel_l2(yf, ref), orc.rel_l2(yf2, ref), orc.rel_l2(yp, ref), orc.rel_l2(yp2, ref))))
     finally:
         dist.destroy_process_group()
 

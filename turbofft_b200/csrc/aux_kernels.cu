@@ -95,14 +95,17 @@ struct PeerPtrs {
 template <typename C, bool TW>
 __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restrict__ src, PeerPtrs<C> dst, long long rows,
                                                                 long long cols, long long cb, long long ld, long long row0,
-                                                                int log_total) {
+                                                                int log_total, int n_peers, long long sub_off, long long sub_len) {
     __shared__ C tile[32][33];
-    const long long tiles_c = cols / 32;
-    const long long tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+    // the launch covers, for every receiver j, the columns j*cb + sub_off + [0, sub_len)
+    const long long ts = sub_len / 32;
+    const long long tr = blockIdx.x / (ts * n_peers);
+    const long long rem = blockIdx.x % (ts * n_peers);
+    const long long c0 = (rem / ts) * cb + sub_off + (rem % ts) * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const long long r = tr * 32 + ty + 8 * k, c = tc * 32 + tx;
+        const long long r = tr * 32 + ty + 8 * k, c = c0 + tx;
         C v = __ldcs(src + r * cols + c);
         if (TW) {
             typedef typename RealOf<C>::type T;
@@ -118,8 +121,7 @@ __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restr
         tile[ty + 8 * k][tx] = v;
     }
     __syncthreads();
-    const long long c0 = tc * 32;
-    C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb is a multiple of 32
+    C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb, sub_off are multiples of 32
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const long long c = c0 + ty + 8 * k;
@@ -175,33 +177,42 @@ int tfft_permute102(const void* src, void* dst, long long A, long long B, long l
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
 }
 
-int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
-                           long long ld_dst, long long row0, int twiddle, int log_total, int dtype, void* stream) {
+int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
+                                long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
+                                long long sub_len, int dtype, void* stream) {
     if (!src || !peer_dst || n_peers < 1 || n_peers > kMaxPeers || rows < 32 || cols < 32 || (rows & 31) || (cols & 31) ||
         cols % n_peers || ((cols / n_peers) & 31) || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
         return TFFT_ERR_BAD_ARG;
     if (twiddle && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
-    const long long blocks = (rows / 32) * (cols / 32);
+    const long long cb = cols / n_peers;
+    if (sub_off < 0 || sub_len < 32 || (sub_off & 31) || (sub_len & 31) || sub_off + sub_len > cb) return TFFT_ERR_BAD_ARG;
+    const long long blocks = (rows / 32) * (sub_len / 32) * n_peers;
     if (blocks > 2147483647LL) return TFFT_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
-    const long long cb = cols / n_peers;
     if (dtype == TFFT_FLOAT2) {
         PeerPtrs<float2> pp;
         for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (float2*)(i < n_peers ? peer_dst[i] : nullptr);
         if (twiddle)
-            scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+            scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
         else
-            scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+            scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
     } else {
         PeerPtrs<double2> pp;
         for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (double2*)(i < n_peers ? peer_dst[i] : nullptr);
         if (twiddle)
-            scatter_transpose_kernel<double2, true><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+            scatter_transpose_kernel<double2, true><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
         else
-            scatter_transpose_kernel<double2, false><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total);
+            scatter_transpose_kernel<double2, false><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
     }
     tfft::note_launch();
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
+                           long long ld_dst, long long row0, int twiddle, int log_total, int dtype, void* stream) {
+    if (n_peers < 1 || cols % n_peers) return TFFT_ERR_BAD_ARG;
+    return tfft_scatter_transpose_part(src, peer_dst, n_peers, rows, cols, ld_dst, row0, twiddle, log_total, 0,
+                                       cols / n_peers, dtype, stream);
 }
 
 // Peer-visible device buffers for the fused exchange: plain cudaMalloc so that the IPC

@@ -218,7 +218,9 @@ class FusedFourStepFFT(FourStepFFT):
     """
 
     def __init__(self, logn: int, world: int, rank: int, dtype_code: int, device_index: int, group=None,
-                 natural_order: bool = False, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1):
+                 natural_order: bool = False, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1, pipeline: int = 1):
+        """pipeline = G > 1 cuts each exchange into G column groups issued on a side stream; the
+        local transforms of group g run on the caller's stream while group g + 1 is in flight."""
         import torch
 
         be = DeviceBackend(dtype_code, device_index, if_ft, if_err, thread_bs)
@@ -230,6 +232,11 @@ class FusedFourStepFFT(FourStepFFT):
         self.bufs = PeerBuffers((self.n1 * self.n2 // world) * self.esize, world, rank, device_index, group)
         self.token = torch.zeros(1, device=f"cuda:{device_index}")
         self._plans = {}
+        self.G = max(1, int(pipeline))
+        if self.G > 1:
+            if (self.n1 // world) % (32 * self.G) or (self.n2 // world) % (32 * self.G):
+                raise ValueError("pipeline groups must hold a multiple of 32 lines")
+            self.side = torch.cuda.Stream(device=device_index)
 
     def _stream(self):
         return self.torch.cuda.current_stream(self.dev).cuda_stream
@@ -241,9 +248,42 @@ class FusedFourStepFFT(FourStepFFT):
 
             dist.all_reduce(self.token, group=self.group)
 
-    def _scatter(self, src_ptr, buf, rows, cols, ld, row0, tw):
-        _lib.check(lib().tfft_scatter_transpose(src_ptr, self.bufs.table(buf), self.world, rows, cols, ld, row0, int(tw),
-                                                self.logn, self.dt, self._stream()), "tfft_scatter_transpose")
+    def _scatter(self, src_ptr, buf, rows, cols, ld, row0, tw, sub_off=None, sub_len=None):
+        if sub_off is None:
+            sub_off, sub_len = 0, cols // self.world
+        _lib.check(lib().tfft_scatter_transpose_part(src_ptr, self.bufs.table(buf), self.world, rows, cols, ld, row0, int(tw),
+                                                     self.logn, sub_off, sub_len, self.dt, self._stream()),
+                   "tfft_scatter_transpose_part")
+
+    def _plan(self, logn, count):
+        from . import Plan
+
+        key = (logn, count)
+        if key not in self._plans:
+            self._plans[key] = Plan(logn, count, self.dt, self.be.if_ft, self.be.if_err, self.be.thread_bs, device=self.dev)
+        return self._plans[key]
+
+    def _exchange_and_transform(self, src, buf, rows, cols, ld, row0, tw, line_log, lines, out):
+        """One pipelined exchange: G scatter pieces + fences on the side stream, and behind each
+        fence the transform of the lines that piece completed, on the caller's stream."""
+        torch, G = self.torch, self.G
+        main = torch.cuda.current_stream(self.dev)
+        self.side.wait_stream(main)
+        piece = (cols // self.world) // G          # lines of the receiver completed by one piece
+        events = []
+        with torch.cuda.stream(self.side):
+            for g in range(G):
+                self._scatter(src.data_ptr(), buf, rows, cols, ld, row0, tw, g * piece, piece)
+                self._fence()
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                events.append(ev)
+        plan = self._plan(line_log, piece)
+        step = piece * (1 << line_log) * self.esize
+        for g in range(G):
+            main.wait_event(events[g])
+            plan.exec_ptr(self.bufs.local[buf] + g * step, out.data_ptr() + g * step, main.cuda_stream)
+        return out
 
     def _fft_from(self, src_ptr, logn, count, out):
         from . import Plan
@@ -258,6 +298,20 @@ class FusedFourStepFFT(FourStepFFT):
         P, r = self.world, self.rank
         n1, n2, n1l, n2l = self.n1, self.n2, self.n1 // P, self.n2 // P
         x_local = x_local.contiguous()
+        if self.G > 1:
+            tmp = self._exchange_and_transform(x_local, 0, n1l, n2, n1, r * n1l, False, self.l1, n2l,
+                                               self.torch.empty_like(x_local))
+            out = self._exchange_and_transform(tmp, 1, n2l, n1, n2, r * n2l, True, self.l2, n1l,
+                                               self.torch.empty_like(x_local))
+            self.torch.cuda.current_stream(self.dev).wait_stream(self.side)
+            if not self.natural:
+                return out
+            self._scatter(out.data_ptr(), 0, n1l, n2, n1, r * n1l, False)
+            self._fence()
+            res = self.torch.empty_like(x_local)
+            _lib.check(lib().tfft_stream_copy(self.bufs.local[0], res.data_ptr(), res.numel() * self.esize, self._stream()),
+                       "tfft_stream_copy")
+            return res
         # 1. x[n1l][N2] -> every rank's buffer 0 as [n2l][N1]
         self._scatter(x_local.data_ptr(), 0, n1l, n2, n1, r * n1l, False)
         self._fence()
