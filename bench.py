@@ -56,7 +56,7 @@ def parse_args():
                          "distributed over the GPUs (four-step, all-to-all over NVLink)")
     ap.add_argument("--logN", type=int, default=30, help="fourstep: log2 of the transform length")
     ap.add_argument("--natural", type=int, default=0, help="fourstep: 1 = natural-order output (third exchange)")
-    ap.add_argument("--pipeline", type=int, default=4, help="fourstep, fused: pieces per exchange overlapped with the local transforms")
+    ap.add_argument("--pipeline", type=int, default=8, help="fourstep, fused: pieces per exchange overlapped with the local transforms")
     ap.add_argument("--fused", type=int, default=1, help="fourstep: 1 = exchanges fused into peer-storing kernels, "
                                                          "0 = NCCL all-to-all between local kernels")
     return ap.parse_args()

@@ -179,10 +179,12 @@ int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, 
 
 /* The same for a slice of every receiver's block: only the columns j * (cols / n_peers) +
  * sub_off + [0, sub_len) of each receiver j (multiples of 32).  Lets a caller cut one
- * exchange into pieces and overlap piece g + 1 with the transform of piece g. */
+ * exchange into pieces and overlap piece g + 1 with the transform of piece g; max_blocks > 0
+ * bounds the grid (the kernel strides over its tiles) so that the NVLink-bound copy holds only
+ * a few slots per SM and the transforms get the rest. */
 int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
                                 long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
-                                long long sub_len, int dtype, void* stream);
+                                long long sub_len, int max_blocks, int dtype, void* stream);
 
 /* Receive buffers other processes can map: cudaMalloc + CUDA IPC handle (64 bytes). */
 int tfft_peer_alloc(size_t bytes, void** ptr);

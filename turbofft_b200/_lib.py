@@ -45,7 +45,7 @@ SIGNATURES = {
                                         C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "tfft_scatter_transpose_part": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_longlong,
                                              C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_int,
-                                             C.c_void_p]),
+                                             C.c_int, C.c_void_p]),
     "tfft_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "tfft_peer_free": (C.c_int, [C.c_void_p]),
     "tfft_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),

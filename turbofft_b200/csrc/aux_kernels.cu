@@ -99,33 +99,39 @@ __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restr
     __shared__ C tile[32][33];
     // the launch covers, for every receiver j, the columns j*cb + sub_off + [0, sub_len)
     const long long ts = sub_len / 32;
-    const long long tr = blockIdx.x / (ts * n_peers);
-    const long long rem = blockIdx.x % (ts * n_peers);
-    const long long c0 = (rem / ts) * cb + sub_off + (rem % ts) * 32;
+    const long long n_tiles = (rows / 32) * ts * n_peers;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    // grid-stride over the tiles: a caller that overlaps this kernel with transforms gives it a
+    // small grid so that it keeps a few slots per SM and leaves the rest to them
+    for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const long long tr = t / (ts * n_peers);
+        const long long rem = t % (ts * n_peers);
+        const long long c0 = (rem / ts) * cb + sub_off + (rem % ts) * 32;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const long long r = tr * 32 + ty + 8 * k, c = c0 + tx;
-        C v = __ldcs(src + r * cols + c);
-        if (TW) {
-            typedef typename RealOf<C>::type T;
-            const unsigned long long mask = (1ULL << log_total) - 1;
-            const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)c) & mask;
-            double sn, cs;
-            sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
-            C w;
-            w.x = (T)(v.x * cs - v.y * sn);
-            w.y = (T)(v.x * sn + v.y * cs);
-            v = w;
+        for (int k = 0; k < 4; ++k) {
+            const long long r = tr * 32 + ty + 8 * k, c = c0 + tx;
+            C v = __ldcs(src + r * cols + c);
+            if (TW) {
+                typedef typename RealOf<C>::type T;
+                const unsigned long long mask = (1ULL << log_total) - 1;
+                const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)c) & mask;
+                double sn, cs;
+                sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
+                C w;
+                w.x = (T)(v.x * cs - v.y * sn);
+                w.y = (T)(v.x * sn + v.y * cs);
+                v = w;
+            }
+            tile[ty + 8 * k][tx] = v;
         }
-        tile[ty + 8 * k][tx] = v;
-    }
-    __syncthreads();
-    C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb, sub_off are multiples of 32
+        __syncthreads();
+        C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb, sub_off are multiples of 32
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const long long c = c0 + ty + 8 * k;
-        base[(c % cb) * ld + row0 + tr * 32 + tx] = tile[tx][ty + 8 * k];
+        for (int k = 0; k < 4; ++k) {
+            const long long c = c0 + ty + 8 * k;
+            base[(c % cb) * ld + row0 + tr * 32 + tx] = tile[tx][ty + 8 * k];
+        }
+        __syncthreads();  // the tile buffer is reused by the next iteration
     }
 }
 
@@ -179,15 +185,16 @@ int tfft_permute102(const void* src, void* dst, long long A, long long B, long l
 
 int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
                                 long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
-                                long long sub_len, int dtype, void* stream) {
+                                long long sub_len, int max_blocks, int dtype, void* stream) {
     if (!src || !peer_dst || n_peers < 1 || n_peers > kMaxPeers || rows < 32 || cols < 32 || (rows & 31) || (cols & 31) ||
         cols % n_peers || ((cols / n_peers) & 31) || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
         return TFFT_ERR_BAD_ARG;
     if (twiddle && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
     const long long cb = cols / n_peers;
     if (sub_off < 0 || sub_len < 32 || (sub_off & 31) || (sub_len & 31) || sub_off + sub_len > cb) return TFFT_ERR_BAD_ARG;
-    const long long blocks = (rows / 32) * (sub_len / 32) * n_peers;
-    if (blocks > 2147483647LL) return TFFT_ERR_TOO_LARGE;
+    long long blocks = (rows / 32) * (sub_len / 32) * n_peers;
+    if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
+    if (blocks > 2147483647LL) blocks = 2147483647LL;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == TFFT_FLOAT2) {
         PeerPtrs<float2> pp;
@@ -212,7 +219,7 @@ int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, 
                            long long ld_dst, long long row0, int twiddle, int log_total, int dtype, void* stream) {
     if (n_peers < 1 || cols % n_peers) return TFFT_ERR_BAD_ARG;
     return tfft_scatter_transpose_part(src, peer_dst, n_peers, rows, cols, ld_dst, row0, twiddle, log_total, 0,
-                                       cols / n_peers, dtype, stream);
+                                       cols / n_peers, 0, dtype, stream);
 }
 
 // Peer-visible device buffers for the fused exchange: plain cudaMalloc so that the IPC

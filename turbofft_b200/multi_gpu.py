@@ -23,6 +23,7 @@ only (remote data always lands in local HBM first).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Tuple
 
 from . import _lib
@@ -236,7 +237,14 @@ class FusedFourStepFFT(FourStepFFT):
         if self.G > 1:
             if (self.n1 // world) % (32 * self.G) or (self.n2 // world) % (32 * self.G):
                 raise ValueError("pipeline groups must hold a multiple of 32 lines")
-            self.side = torch.cuda.Stream(device=device_index)
+            # the exchange pieces run at low priority, the transforms behind them at high priority:
+            # otherwise the blocks of piece g + 1, already queued, keep the transform of piece g
+            # off the SMs until they have drained and nothing overlaps
+            self.side = torch.cuda.Stream(device=device_index, priority=0)
+            self.fast = torch.cuda.Stream(device=device_index, priority=-1)
+            # the exchange kernel is NVLink bound: a few resident blocks per SM saturate the links
+            sms = torch.cuda.get_device_properties(device_index).multi_processor_count
+            self.copy_blocks = int(os.environ.get("TFFT_EXCHANGE_BLOCKS_PER_SM", "4")) * sms
 
     def _stream(self):
         return self.torch.cuda.current_stream(self.dev).cuda_stream
@@ -248,11 +256,11 @@ class FusedFourStepFFT(FourStepFFT):
 
             dist.all_reduce(self.token, group=self.group)
 
-    def _scatter(self, src_ptr, buf, rows, cols, ld, row0, tw, sub_off=None, sub_len=None):
+    def _scatter(self, src_ptr, buf, rows, cols, ld, row0, tw, sub_off=None, sub_len=None, max_blocks=0):
         if sub_off is None:
             sub_off, sub_len = 0, cols // self.world
         _lib.check(lib().tfft_scatter_transpose_part(src_ptr, self.bufs.table(buf), self.world, rows, cols, ld, row0, int(tw),
-                                                     self.logn, sub_off, sub_len, self.dt, self._stream()),
+                                                     self.logn, sub_off, sub_len, max_blocks, self.dt, self._stream()),
                    "tfft_scatter_transpose_part")
 
     def _plan(self, logn, count):
@@ -273,16 +281,18 @@ class FusedFourStepFFT(FourStepFFT):
         events = []
         with torch.cuda.stream(self.side):
             for g in range(G):
-                self._scatter(src.data_ptr(), buf, rows, cols, ld, row0, tw, g * piece, piece)
+                self._scatter(src.data_ptr(), buf, rows, cols, ld, row0, tw, g * piece, piece, self.copy_blocks)
                 self._fence()
                 ev = torch.cuda.Event()
                 ev.record(self.side)
                 events.append(ev)
         plan = self._plan(line_log, piece)
         step = piece * (1 << line_log) * self.esize
+        self.fast.wait_stream(main)
         for g in range(G):
-            main.wait_event(events[g])
-            plan.exec_ptr(self.bufs.local[buf] + g * step, out.data_ptr() + g * step, main.cuda_stream)
+            self.fast.wait_event(events[g])
+            plan.exec_ptr(self.bufs.local[buf] + g * step, out.data_ptr() + g * step, self.fast.cuda_stream)
+        main.wait_stream(self.fast)
         return out
 
     def _fft_from(self, src_ptr, logn, count, out):
