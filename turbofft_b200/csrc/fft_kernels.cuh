@@ -220,10 +220,11 @@ struct Cfg {
     static constexpr size_t smem_bytes(int ft) { return SMEM_BYTES + (ft == FT_CSUM ? (size_t)2 * M * C * 2 * sizeof(T) : 0); }
     // Occupancy target handed to the compiler as the register cap: enough blocks for
     // 1024 (fp32) / 512 (fp64) resident threads per SM unless shared memory allows fewer.
-    // The FT variants carry the checksum state on top and get a quarter more registers.
+    // The FT variants carry the checksum state on top and get a quarter more registers;
+    // 32 points per thread need twice the registers, so half the threads.
     static constexpr int SMEM_BLOCKS = SMEM_BYTES ? (int)((220 * 1024) / SMEM_BYTES) : 32;
     static constexpr int min_blocks(bool ft) {
-        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? TFFT_FT_OCC : 4) / 4;
+        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? TFFT_FT_OCC : 4) / 4 / (LOGE == 5 ? 2 : 1);
         const int tb = (target + THREADS - 1) / THREADS;
         const int b = SMEM_BLOCKS < tb ? SMEM_BLOCKS : tb;
         return b < 1 ? 1 : b;

@@ -58,8 +58,9 @@ def candidates(logn: int, datatype: str):
             b = logn - a
             if not 6 <= b <= 12 or abs(a - b) > 3:
                 continue
-            for e1 in (8, 16):
-                for e2 in (8, 16):
+            # 32 points per thread only where it saves an exchange (lines of 512 and 1024)
+            for e1 in es if a in (9, 10) else (8, 16):
+                for e2 in es if b in (9, 10) else (8, 16):
                     for c1 in (4, 8, 16, 32):
                         for c2 in (4, 8, 16, 32):
                             if c2 > (1 << a):
