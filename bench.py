@@ -403,7 +403,24 @@ def run_ours(a):
             e_ms = float(t.item())
         e2e = {"value": world * flops_step / (e_ms * 1e-3) / 1e9, "unit": "GFLOPS",
                "h2d_bytes_per_step": int(len(points) * n * esize), "d2h_bytes_per_step": int(len(points) * n * esize),
-               "steps": a.e2e_steps, "ms_per_step": e_ms, "api": "tfft_exec_host (pinned host buffers)"}
+               "steps": a.e2e_steps, "ms_per_step": e_ms, "api": "tfft_exec_host (pinned host buffers)",
+               "pcie_gbs_per_direction": len(points) * n * esize / (e_ms * 1e-3) / 1e9}
+        # what this host and link give two plain concurrent copies (one per direction), for scale
+        s_up, s_dn = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        half = host_in.numel() // 2
+        d_up, d_dn = torch.empty_like(x[:half]), x[half:2 * half]
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            with torch.cuda.stream(s_up):
+                d_up.copy_(host_in[:half], non_blocking=True)
+            with torch.cuda.stream(s_dn):
+                host_out[:half].copy_(d_dn, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        e2e["pcie_duplex_copy_gbs_per_direction_same_run"] = half * esize / best / 1e9
 
     if rank != 0:
         if dist is not None:

@@ -100,6 +100,7 @@ struct tfft_plan_s {
     tfft_plan chunk_plan = nullptr;
     tfft_plan tail_plan = nullptr;
     long long chunk_batch = 0;
+    bool pipe_ready = false;  // sub-plans, streams and events of the pipelined host path all exist
     cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_in[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_fft[3] = {nullptr, nullptr, nullptr};
@@ -435,24 +436,33 @@ static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host,
     const size_t sig_bytes = ((size_t)1 << p->logn) * p->esize();
     long long cb = (long long)(kPipeChunkBytes / sig_bytes);
     if (p->if_ft || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
-    if (!p->chunk_plan) {
+    if (!p->pipe_ready) {
+        // every resource is created only if it is still missing, so a call that failed half way
+        // can be repeated; the plan's destructor releases whatever exists
         const char* csv = p->param_csv.empty() ? nullptr : p->param_csv.c_str();
-        int rc = tfft_plan_create(&p->chunk_plan, p->logn, cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
-        if (rc != TFFT_OK) return rc;
-        p->chunk_batch = cb;
-        if (p->batch % cb) {
-            rc = tfft_plan_create(&p->tail_plan, p->logn, p->batch % cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
+        if (!p->chunk_plan) {
+            const int rc = tfft_plan_create(&p->chunk_plan, p->logn, cb, p->dtype, 0, 0, p->thread_bs, csv, p->device);
+            if (rc != TFFT_OK) return rc;
+            p->chunk_batch = cb;
+        }
+        if (p->batch % p->chunk_batch && !p->tail_plan) {
+            const int rc = tfft_plan_create(&p->tail_plan, p->logn, p->batch % p->chunk_batch, p->dtype, 0, 0,
+                                            p->thread_bs, csv, p->device);
             if (rc != TFFT_OK) return rc;
         }
         tfft_set_direction(p, p->inverse, p->scale);  // hand the direction down to the sub-plans
         for (int i = 0; i < 3; ++i) {
-            if (!cuda_ok(p, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking))) return TFFT_ERR_CUDA;
-            if (!cuda_ok(p, cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming)) ||
-                !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_fft[i], cudaEventDisableTiming)) ||
-                !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_out[i], cudaEventDisableTiming)))
+            if (!p->pipe_stream[i] &&
+                !cuda_ok(p, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking)))
+                return TFFT_ERR_CUDA;
+            if ((!p->ev_in[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming))) ||
+                (!p->ev_fft[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_fft[i], cudaEventDisableTiming))) ||
+                (!p->ev_out[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_out[i], cudaEventDisableTiming))))
                 return TFFT_ERR_CUDA;
         }
-        if (!cuda_ok(p, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming))) return TFFT_ERR_CUDA;
+        if (!p->ev_start && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming)))
+            return TFFT_ERR_CUDA;
+        p->pipe_ready = true;
     }
     cb = p->chunk_batch;
     const size_t chunk_bytes = (size_t)cb * sig_bytes;
