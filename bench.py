@@ -56,6 +56,8 @@ def parse_args():
                          "distributed over the GPUs (four-step, all-to-all over NVLink)")
     ap.add_argument("--logN", type=int, default=30, help="fourstep: log2 of the transform length")
     ap.add_argument("--natural", type=int, default=0, help="fourstep: 1 = natural-order output (third exchange)")
+    ap.add_argument("--exchange", default="stores", choices=["stores", "dma"],
+                    help="fourstep, fused, pipelined: peer stores from the transposing kernel, or pack + copy-engine copies")
     ap.add_argument("--pipeline", type=int, default=8, help="fourstep, fused: pieces per exchange overlapped with the local transforms")
     ap.add_argument("--fused", type=int, default=1, help="fourstep: 1 = exchanges fused into peer-storing kernels, "
                                                          "0 = NCCL all-to-all between local kernels")
@@ -493,7 +495,8 @@ def run_fourstep(a):
     x = torch.view_as_complex(torch.rand(n_local, 2, generator=g, device=dev, dtype=rdtype) * 2 - 1).to(tdtype)
     if a.fused:
         fs = mg.FusedFourStepFFT(a.logN, world, rank, a.datatype, local, natural_order=bool(a.natural),
-                                 if_ft=int(a.ft >= 1), if_err=int(a.ft == 2), thread_bs=a.thread_bs, pipeline=a.pipeline)
+                                 if_ft=int(a.ft >= 1), if_err=int(a.ft == 2), thread_bs=a.thread_bs, pipeline=a.pipeline,
+                                 exchange=a.exchange)
         be = fs
     else:
         be = mg.DeviceBackend(a.datatype, local, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2), thread_bs=a.thread_bs)
@@ -539,7 +542,7 @@ def run_fourstep(a):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32" if a.datatype == 0 else "f64", "data": "synthetic",
             "config": {"workload": f"cfg5: one 2^{a.logN}-point C2C transform as 2^{fs.l1} x 2^{fs.l2}, four-step over "
                                    f"{world} GPU(s), {'natural' if a.natural else 'transposed'} output, FT {'on' if a.ft else 'off'}, "
-                                   f"{'exchange fused into peer-storing transpose kernels, %d pieces pipelined' % a.pipeline if a.fused else 'NCCL all_to_all_single'}",
+                                   f"{('exchange fused into peer-storing transpose kernels' if a.exchange == 'stores' else 'pack kernel + copy-engine peer copies') + ', %d pieces pipelined' % a.pipeline if a.fused else 'NCCL all_to_all_single'}",
                        "exchanges": (3 if a.natural else 2) if world > 1 else 0,
                        "nvlink_bytes_per_exchange_per_gpu": int((world - 1) / world * n * esize / world)},
             "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",

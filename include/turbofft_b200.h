@@ -186,6 +186,22 @@ int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_pe
                                 long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
                                 long long sub_len, int max_blocks, int dtype, void* stream);
 
+/* General form: receiver j's buffer has its own line pitch dst_ld[j] and this sender's rows
+ * start at dst_row0[j] inside a line; the twiddle uses the global row index tw_row0 + i.  With
+ * local staging buffers as "receivers" (pitch = rows, offset 0) the kernel becomes the pack
+ * step of a copy-engine exchange: the packed block of receiver j is then moved by
+ * tfft_copy_2d.  complex64 twiddles support log_total <= 39.  No counterpart in the
+ * reference (single GPU). */
+int tfft_scatter_transpose_ex(const void* src, void* const* dst, const long long* dst_ld, const long long* dst_row0,
+                              int n_peers, long long rows, long long cols, long long tw_row0, int twiddle, int log_total,
+                              long long sub_off, long long sub_len, int max_blocks, int dtype, void* stream);
+
+/* Stream-ordered 2-D copy between any two device buffers this process can address (its own
+ * or peer mappings): height rows of width bytes, pitches in bytes.  Runs on the copy engines,
+ * so it takes no SM from the transforms it overlaps with. */
+int tfft_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width, size_t height,
+                 void* stream);
+
 /* Receive buffers other processes can map: cudaMalloc + CUDA IPC handle (64 bytes). */
 int tfft_peer_alloc(size_t bytes, void** ptr);
 int tfft_peer_free(void* ptr);

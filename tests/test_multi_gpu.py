@@ -200,7 +200,15 @@ def _gpu_worker(rank, world, port, logn, dtype, q):
         torch.cuda.synchronize()
         dist.barrier()
         piped.close()
-        q.put((rank, max(orc.rel_l2(y, ref), orc.rel_l2(yf, ref), orc.rel_l2(yf2, ref), orc.rel_l2(yp, ref), orc.rel_l2(yp2, ref))))
+        # and with the copy engines moving the packed pieces
+        dma = mg.FusedFourStepFFT(logn, world, rank, dtype, rank, natural_order=True, if_ft=1, pipeline=2, exchange="dma")
+        yd = dma(xg).cpu().numpy()
+        yd2 = dma(xg).cpu().numpy()
+        torch.cuda.synchronize()
+        dist.barrier()
+        dma.close()
+        q.put((rank, max(orc.rel_l2(y, ref), orc.rel_l2(yf, ref), orc.rel_l2(yf2, ref), orc.rel_l2(yp, ref), orc.rel_l2(yp2, ref),
+                         orc.rel_l2(yd, ref), orc.rel_l2(yd2, ref))))
     finally:
         dist.destroy_process_group()
 

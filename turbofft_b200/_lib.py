@@ -46,6 +46,10 @@ SIGNATURES = {
     "tfft_scatter_transpose_part": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_longlong,
                                              C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_int,
                                              C.c_int, C.c_void_p]),
+    "tfft_scatter_transpose_ex": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong),
+                                           C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, C.c_int, C.c_int, C.c_longlong,
+                                           C.c_longlong, C.c_int, C.c_int, C.c_void_p]),
+    "tfft_copy_2d": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]),
     "tfft_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "tfft_peer_free": (C.c_int, [C.c_void_p]),
     "tfft_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),

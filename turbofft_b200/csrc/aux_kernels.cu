@@ -27,9 +27,26 @@ template <typename C> struct RealOf;
 template <> struct RealOf<float2> { typedef float type; };
 template <> struct RealOf<double2> { typedef double type; };
 
+// exp(-2*pi*i*ph / 2^log_total).  Single precision splits the phase into two exactly
+// representable angles (high and low 15 bits) and multiplies the two unit vectors, which keeps
+// float accuracy for totals up to 2^30 without double-precision arithmetic.
+__device__ __forceinline__ float2 unit_twiddle(unsigned long long ph, int log_total, float) {
+    const int lo_bits = log_total > 15 ? log_total - 15 : 0;
+    const unsigned long long hi = ph >> lo_bits, lo = ph & ((1ULL << lo_bits) - 1);
+    float s1, c1, s2, c2;
+    sincospif(-2.0f * (float)hi / (float)(1ULL << (log_total - lo_bits)), &s1, &c1);
+    sincospif(-2.0f * (float)lo / (float)(1ULL << log_total), &s2, &c2);
+    return make_float2(c1 * c2 - s1 * s2, s1 * c2 + c1 * s2);
+}
+__device__ __forceinline__ double2 unit_twiddle(unsigned long long ph, int log_total, double) {
+    double sn, cs;
+    sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
+    return make_double2(cs, sn);
+}
+
 // 32x32 tile transpose through padded shared memory; TW multiplies by
-// exp(-2*pi*i*(row0+r)*(col0+c)/2^log_total), evaluated with sincospi in double so
-// that the integer phase (r*c mod 2^log_total) is reduced exactly.
+// exp(-2*pi*i*(row0+r)*(col0+c)/2^log_total); the integer phase (r*c mod 2^log_total) is
+// reduced exactly before the angle is formed.
 template <typename C, bool TW>
 __global__ void __launch_bounds__(256) transpose_kernel(const C* __restrict__ src, C* __restrict__ dst, long long rows,
                                                         long long cols, long long row0, long long col0, int log_total) {
@@ -46,11 +63,10 @@ __global__ void __launch_bounds__(256) transpose_kernel(const C* __restrict__ sr
                 typedef typename RealOf<C>::type T;
                 const unsigned long long mask = (1ULL << log_total) - 1;
                 const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)(col0 + c)) & mask;
-                double sn, cs;
-                sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
+                const C u = unit_twiddle(ph, log_total, T(0));
                 C w;
-                w.x = (T)(v.x * cs - v.y * sn);
-                w.y = (T)(v.x * sn + v.y * cs);
+                w.x = v.x * u.x - v.y * u.y;
+                w.y = v.x * u.y + v.y * u.x;
                 v = w;
             }
             tile[ty + 8 * k][tx] = v;
@@ -90,11 +106,14 @@ constexpr int kMaxPeers = 16;
 template <typename C>
 struct PeerPtrs {
     C* p[kMaxPeers];
+    long long ld[kMaxPeers];    // line pitch of receiver j's buffer, in elements
+    long long roff[kMaxPeers];  // where this sender's rows start inside a line of receiver j
 };
+
 
 template <typename C, bool TW>
 __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restrict__ src, PeerPtrs<C> dst, long long rows,
-                                                                long long cols, long long cb, long long ld, long long row0,
+                                                                long long cols, long long cb, long long row0,
                                                                 int log_total, int n_peers, long long sub_off, long long sub_len) {
     __shared__ C tile[32][33];
     // the launch covers, for every receiver j, the columns j*cb + sub_off + [0, sub_len)
@@ -107,29 +126,41 @@ __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restr
         const long long tr = t / (ts * n_peers);
         const long long rem = t % (ts * n_peers);
         const long long c0 = (rem / ts) * cb + sub_off + (rem % ts) * 32;
+        const long long c = c0 + tx;
+        // a thread's four rows are 8 apart: w_k = w_0 * (W^(8c))^k, two evaluations instead of four
+        C w, step;
+        if (TW) {
+            typedef typename RealOf<C>::type T;
+            const unsigned long long mask = (1ULL << log_total) - 1;
+            w = unit_twiddle(((unsigned long long)(row0 + tr * 32 + ty) * (unsigned long long)c) & mask, log_total, T(0));
+            step = unit_twiddle((8ULL * (unsigned long long)c) & mask, log_total, T(0));
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const long long r = tr * 32 + ty + 8 * k, c = c0 + tx;
+            const long long r = tr * 32 + ty + 8 * k;
             C v = __ldcs(src + r * cols + c);
             if (TW) {
-                typedef typename RealOf<C>::type T;
-                const unsigned long long mask = (1ULL << log_total) - 1;
-                const unsigned long long ph = ((unsigned long long)(row0 + r) * (unsigned long long)c) & mask;
-                double sn, cs;
-                sincospi(-2.0 * (double)ph / (double)(1ULL << log_total), &sn, &cs);
-                C w;
-                w.x = (T)(v.x * cs - v.y * sn);
-                w.y = (T)(v.x * sn + v.y * cs);
-                v = w;
+                C u;
+                u.x = v.x * w.x - v.y * w.y;
+                u.y = v.x * w.y + v.y * w.x;
+                v = u;
+                if (k < 3) {
+                    C n;
+                    n.x = w.x * step.x - w.y * step.y;
+                    n.y = w.x * step.y + w.y * step.x;
+                    w = n;
+                }
             }
             tile[ty + 8 * k][tx] = v;
         }
         __syncthreads();
-        C* base = dst.p[c0 / cb];  // a tile never straddles two receivers: cb, sub_off are multiples of 32
+        const int j = (int)(c0 / cb);  // a tile never straddles two receivers: cb, sub_off are multiples of 32
+        C* base = dst.p[j] + dst.roff[j] + tr * 32 + tx;
+        const long long ld = dst.ld[j];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const long long c = c0 + ty + 8 * k;
-            base[(c % cb) * ld + row0 + tr * 32 + tx] = tile[tx][ty + 8 * k];
+            base[(c % cb) * ld] = tile[tx][ty + 8 * k];
         }
         __syncthreads();  // the tile buffer is reused by the next iteration
     }
@@ -139,7 +170,7 @@ template <bool TW>
 int launch_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
                      int log_total, int dtype, void* stream) {
     if (!src || !dst || rows < 1 || cols < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2)) return TFFT_ERR_BAD_ARG;
-    if (TW && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
+    if (TW && (log_total < 1 || log_total > 62 || (dtype == TFFT_FLOAT2 && log_total > 39))) return TFFT_ERR_BAD_ARG;
     const long long blocks = ((rows + 31) / 32) * ((cols + 31) / 32);
     if (blocks > 2147483647LL) return TFFT_ERR_TOO_LARGE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -183,36 +214,69 @@ int tfft_permute102(const void* src, void* dst, long long A, long long B, long l
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
 }
 
-int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
-                                long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
-                                long long sub_len, int max_blocks, int dtype, void* stream) {
-    if (!src || !peer_dst || n_peers < 1 || n_peers > kMaxPeers || rows < 32 || cols < 32 || (rows & 31) || (cols & 31) ||
-        cols % n_peers || ((cols / n_peers) & 31) || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
+int tfft_scatter_transpose_ex(const void* src, void* const* dst, const long long* dst_ld, const long long* dst_row0,
+                              int n_peers, long long rows, long long cols, long long tw_row0, int twiddle, int log_total,
+                              long long sub_off, long long sub_len, int max_blocks, int dtype, void* stream) {
+    if (!src || !dst || !dst_ld || !dst_row0 || n_peers < 1 || n_peers > kMaxPeers || rows < 32 || cols < 32 ||
+        (rows & 31) || (cols & 31) || cols % n_peers || ((cols / n_peers) & 31) ||
+        (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2))
         return TFFT_ERR_BAD_ARG;
-    if (twiddle && (log_total < 1 || log_total > 62)) return TFFT_ERR_BAD_ARG;
+    if (twiddle && (log_total < 1 || log_total > 62 || (dtype == TFFT_FLOAT2 && log_total > 39))) return TFFT_ERR_BAD_ARG;
     const long long cb = cols / n_peers;
     if (sub_off < 0 || sub_len < 32 || (sub_off & 31) || (sub_len & 31) || sub_off + sub_len > cb) return TFFT_ERR_BAD_ARG;
+    for (int i = 0; i < n_peers; ++i)
+        if (!dst[i] || dst_ld[i] < rows || dst_row0[i] < 0 || dst_row0[i] + rows > dst_ld[i]) return TFFT_ERR_BAD_ARG;
     long long blocks = (rows / 32) * (sub_len / 32) * n_peers;
     if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
     if (blocks > 2147483647LL) blocks = 2147483647LL;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == TFFT_FLOAT2) {
         PeerPtrs<float2> pp;
-        for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (float2*)(i < n_peers ? peer_dst[i] : nullptr);
+        for (int i = 0; i < kMaxPeers; ++i) {
+            pp.p[i] = (float2*)(i < n_peers ? dst[i] : nullptr);
+            pp.ld[i] = i < n_peers ? dst_ld[i] : 0;
+            pp.roff[i] = i < n_peers ? dst_row0[i] : 0;
+        }
         if (twiddle)
-            scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
+            scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
         else
-            scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
+            scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
     } else {
         PeerPtrs<double2> pp;
-        for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = (double2*)(i < n_peers ? peer_dst[i] : nullptr);
+        for (int i = 0; i < kMaxPeers; ++i) {
+            pp.p[i] = (double2*)(i < n_peers ? dst[i] : nullptr);
+            pp.ld[i] = i < n_peers ? dst_ld[i] : 0;
+            pp.roff[i] = i < n_peers ? dst_row0[i] : 0;
+        }
         if (twiddle)
-            scatter_transpose_kernel<double2, true><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
+            scatter_transpose_kernel<double2, true><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
         else
-            scatter_transpose_kernel<double2, false><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, ld_dst, row0, log_total, n_peers, sub_off, sub_len);
+            scatter_transpose_kernel<double2, false><<<(unsigned)blocks, 256, 0, st>>>((const double2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
     }
     tfft::note_launch();
     return cudaGetLastError() == cudaSuccess ? TFFT_OK : TFFT_ERR_CUDA;
+}
+
+int tfft_scatter_transpose_part(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,
+                                long long ld_dst, long long row0, int twiddle, int log_total, long long sub_off,
+                                long long sub_len, int max_blocks, int dtype, void* stream) {
+    if (n_peers < 1 || n_peers > kMaxPeers) return TFFT_ERR_BAD_ARG;
+    long long ld[kMaxPeers], r0[kMaxPeers];
+    for (int i = 0; i < n_peers; ++i) {
+        ld[i] = ld_dst;
+        r0[i] = row0;
+    }
+    return tfft_scatter_transpose_ex(src, peer_dst, ld, r0, n_peers, rows, cols, row0, twiddle, log_total, sub_off, sub_len,
+                                     max_blocks, dtype, stream);
+}
+
+int tfft_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width, size_t height,
+                 void* stream) {
+    if (!dst || !src || !width || !height || dst_pitch < width || src_pitch < width) return TFFT_ERR_BAD_ARG;
+    return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, height, cudaMemcpyDefault, (cudaStream_t)stream) ==
+                   cudaSuccess
+               ? TFFT_OK
+               : TFFT_ERR_CUDA;
 }
 
 int tfft_scatter_transpose(const void* src, void* const* peer_dst, int n_peers, long long rows, long long cols,

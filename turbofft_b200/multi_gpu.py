@@ -219,9 +219,15 @@ class FusedFourStepFFT(FourStepFFT):
     """
 
     def __init__(self, logn: int, world: int, rank: int, dtype_code: int, device_index: int, group=None,
-                 natural_order: bool = False, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1, pipeline: int = 1):
+                 natural_order: bool = False, if_ft: int = 0, if_err: int = 0, thread_bs: int = 1, pipeline: int = 1,
+                 exchange: str = "stores"):
         """pipeline = G > 1 cuts each exchange into G column groups issued on a side stream; the
-        local transforms of group g run on the caller's stream while group g + 1 is in flight."""
+        local transforms of group g run on the caller's stream while group g + 1 is in flight.
+
+        exchange (pipelined form only): "stores" = the transposing kernel stores into the peers'
+        buffers itself; "dma" = it packs into a local send buffer (own share straight into the own
+        receive buffer) and the copy engines move each peer's block with one 2-D copy, which leaves
+        the SMs to the transforms."""
         import torch
 
         be = DeviceBackend(dtype_code, device_index, if_ft, if_err, thread_bs)
@@ -245,6 +251,16 @@ class FusedFourStepFFT(FourStepFFT):
             # the exchange kernel is NVLink bound: a few resident blocks per SM saturate the links
             sms = torch.cuda.get_device_properties(device_index).multi_processor_count
             self.copy_blocks = int(os.environ.get("TFFT_EXCHANGE_BLOCKS_PER_SM", "4")) * sms
+        if exchange not in ("stores", "dma"):
+            raise ValueError("exchange must be 'stores' or 'dma'")
+        self.exchange = exchange if self.G > 1 and world > 1 else "stores"
+        if self.exchange == "dma":
+            self.send = torch.empty((self.n1 * self.n2 // world) * self.esize, dtype=torch.uint8, device=f"cuda:{device_index}")
+            self.copy = torch.cuda.Stream(device=device_index, priority=0)
+            self.fence_stream = torch.cuda.Stream(device=device_index, priority=-1)
+            # here the pack kernels feed the copy engines, so they go first and the transforms fill in
+            self.side = torch.cuda.Stream(device=device_index, priority=-1)
+            self.fast = torch.cuda.Stream(device=device_index, priority=0)
 
     def _stream(self):
         return self.torch.cuda.current_stream(self.dev).cuda_stream
@@ -295,6 +311,56 @@ class FusedFourStepFFT(FourStepFFT):
         main.wait_stream(self.fast)
         return out
 
+    def _exchange_dma(self, src, buf, rows, cols, ld, row0, tw, line_log, out):
+        """The pipelined exchange with the copy engines as movers.  Piece g: (side stream) pack
+        kernel -> (copy stream) one 2-D copy per peer, nearest rank first so that no two senders
+        aim at one receiver at a time -> (fence stream) barrier -> (fast stream) transform."""
+        torch, G, P, r, es = self.torch, self.G, self.world, self.rank, self.esize
+        main = torch.cuda.current_stream(self.dev)
+        for s in (self.side, self.copy, self.fence_stream, self.fast):
+            s.wait_stream(main)
+        cb = cols // P
+        piece = cb // G
+        # "receivers" of the pack kernel: the send buffer's block for peer j (pitch rows), the own
+        # receive buffer for j == rank (pitch ld, offset row0)
+        ptrs = (C.c_void_p * P)(*[self.bufs.local[buf] if j == r else self.send.data_ptr() + j * cb * rows * es
+                                  for j in range(P)])
+        lds = (C.c_longlong * P)(*[ld if j == r else rows for j in range(P)])
+        offs = (C.c_longlong * P)(*[row0 if j == r else 0 for j in range(P)])
+        events = []
+        for g in range(G):
+            with torch.cuda.stream(self.side):
+                _lib.check(lib().tfft_scatter_transpose_ex(src.data_ptr(), ptrs, lds, offs, P, rows, cols, row0, int(tw),
+                                                           self.logn, g * piece, piece, 0, self.dt, self.side.cuda_stream),
+                           "tfft_scatter_transpose_ex")
+                packed = torch.cuda.Event()
+                packed.record(self.side)
+            self.copy.wait_event(packed)
+            for k in range(1, P):
+                j = (r + k) % P
+                dst = self.bufs.peers[buf][j] + (g * piece * ld + row0) * es
+                srcp = self.send.data_ptr() + (j * cb + g * piece) * rows * es
+                _lib.check(lib().tfft_copy_2d(dst, ld * es, srcp, rows * es, rows * es, piece, self.copy.cuda_stream),
+                           "tfft_copy_2d")
+            sent = torch.cuda.Event()
+            sent.record(self.copy)
+            self.fence_stream.wait_event(sent)
+            with torch.cuda.stream(self.fence_stream):
+                self._fence()
+                ev = torch.cuda.Event()
+                ev.record(self.fence_stream)
+            events.append(ev)
+        plan = self._plan(line_log, piece)
+        step = piece * (1 << line_log) * es
+        for g in range(G):
+            self.fast.wait_event(events[g])
+            plan.exec_ptr(self.bufs.local[buf] + g * step, out.data_ptr() + g * step, self.fast.cuda_stream)
+        main.wait_stream(self.fast)
+        main.wait_stream(self.side)
+        main.wait_stream(self.copy)
+        main.wait_stream(self.fence_stream)
+        return out
+
     def _fft_from(self, src_ptr, logn, count, out):
         from . import Plan
 
@@ -309,10 +375,14 @@ class FusedFourStepFFT(FourStepFFT):
         n1, n2, n1l, n2l = self.n1, self.n2, self.n1 // P, self.n2 // P
         x_local = x_local.contiguous()
         if self.G > 1:
-            tmp = self._exchange_and_transform(x_local, 0, n1l, n2, n1, r * n1l, False, self.l1, n2l,
-                                               self.torch.empty_like(x_local))
-            out = self._exchange_and_transform(tmp, 1, n2l, n1, n2, r * n2l, True, self.l2, n1l,
-                                               self.torch.empty_like(x_local))
+            if self.exchange == "dma":
+                tmp = self._exchange_dma(x_local, 0, n1l, n2, n1, r * n1l, False, self.l1, self.torch.empty_like(x_local))
+                out = self._exchange_dma(tmp, 1, n2l, n1, n2, r * n2l, True, self.l2, self.torch.empty_like(x_local))
+            else:
+                tmp = self._exchange_and_transform(x_local, 0, n1l, n2, n1, r * n1l, False, self.l1, n2l,
+                                                   self.torch.empty_like(x_local))
+                out = self._exchange_and_transform(tmp, 1, n2l, n1, n2, r * n2l, True, self.l2, n1l,
+                                                   self.torch.empty_like(x_local))
             self.torch.cuda.current_stream(self.dev).wait_stream(self.side)
             if not self.natural:
                 return out
