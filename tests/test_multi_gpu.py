@@ -233,3 +233,58 @@ def test_four_step_two_gpus(torch_cuda, dtype, logn):
     res = dict(q.get(timeout=10) for _ in range(2))
     tol = orc.tolerance(np.complex64 if dtype == 0 else np.complex128, logn)
     assert all(e <= tol for e in res.values()), res
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,twiddle", [(0, 0), (0, 1), (1, 1)])
+def test_pack_and_copy_exchange_single_gpu(torch_cuda, dtype, twiddle):
+    """The copy-engine exchange on one device: two receivers, receiver 0 written directly (own share),
+    receiver 1 through a packed send block and one 2-D copy; both must hold what the storing kernel
+    leaves there, and that must be the numpy statement of the exchange."""
+    import ctypes as C
+
+    from turbofft_b200 import _lib
+    from turbofft_b200._lib import lib
+
+    torch = torch_cuda
+    tdt = torch.complex64 if dtype == 0 else torch.complex128
+    es = 8 if dtype == 0 else 16
+    rows, cols, P, ld, row0, log_total = 64, 256, 2, 192, 64, 20
+    cb = cols // P
+    x = torch.randn(rows * cols, dtype=tdt, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    # reference: the storing kernel into two receive buffers of pitch ld
+    direct = [torch.zeros(cb * ld, dtype=tdt, device="cuda") for _ in range(P)]
+    tab = (C.c_void_p * P)(*[d.data_ptr() for d in direct])
+    _lib.check(lib().tfft_scatter_transpose_part(x.data_ptr(), tab, P, rows, cols, ld, row0, twiddle, log_total, 0, cb, 0,
+                                                 dtype, stream), "tfft_scatter_transpose_part")
+    # pack: receiver 0 in place, receiver 1 into a send block of pitch rows; then the 2-D copy, in two pieces
+    recv = [torch.zeros(cb * ld, dtype=tdt, device="cuda") for _ in range(P)]
+    send = torch.zeros(cb * rows, dtype=tdt, device="cuda")
+    ptrs = (C.c_void_p * P)(recv[0].data_ptr(), send.data_ptr())
+    lds = (C.c_longlong * P)(ld, rows)
+    offs = (C.c_longlong * P)(row0, 0)
+    for piece in range(2):
+        sub = cb // 2
+        _lib.check(lib().tfft_scatter_transpose_ex(x.data_ptr(), ptrs, lds, offs, P, rows, cols, row0, twiddle, log_total,
+                                                   piece * sub, sub, 0, dtype, stream), "tfft_scatter_transpose_ex")
+        _lib.check(lib().tfft_copy_2d(recv[1].data_ptr() + (piece * sub * ld + row0) * es, ld * es,
+                                      send.data_ptr() + piece * sub * rows * es, rows * es, rows * es, sub, stream),
+                   "tfft_copy_2d")
+    torch.cuda.synchronize()
+    for j in range(P):
+        assert torch.equal(recv[j], direct[j])
+    xm = x.view(rows, cols).cpu().numpy()
+    if twiddle:
+        r = np.arange(rows)[:, None] + row0
+        c = np.arange(cols)[None, :]
+        xm = xm * np.exp(-2j * np.pi * ((r * c) % (1 << log_total)) / (1 << log_total))
+    for j in range(P):
+        got = recv[j].view(cb, ld).cpu().numpy()[:, row0:row0 + rows]
+        want = xm[:, j * cb:(j + 1) * cb].T
+        assert np.abs(got - want).max() <= (2e-6 if dtype == 0 else 1e-14) * np.abs(want).max()
+    # bad arguments are refused
+    assert lib().tfft_copy_2d(None, 8, send.data_ptr(), 8, 8, 1, stream) != 0
+    bad = (C.c_longlong * P)(rows - 1, rows)
+    assert lib().tfft_scatter_transpose_ex(x.data_ptr(), ptrs, bad, offs, P, rows, cols, row0, twiddle, log_total, 0, cb, 0,
+                                           dtype, stream) != 0
