@@ -288,3 +288,26 @@ def test_pack_and_copy_exchange_single_gpu(torch_cuda, dtype, twiddle):
     bad = (C.c_longlong * P)(rows - 1, rows)
     assert lib().tfft_scatter_transpose_ex(x.data_ptr(), ptrs, bad, offs, P, rows, cols, row0, twiddle, log_total, 0, cb, 0,
                                            dtype, stream) != 0
+
+
+def test_dma_exchange_geometry_numpy():
+    """The copy-engine exchange restated with numpy arrays for 4 ranks: pack per receiver, move every
+    piece with the offsets dma_piece_geometry gives, and compare every receive buffer with the plain
+    statement of the exchange (receiver j holds columns j*cb.. of everybody's rows, transposed)."""
+    P, G = 4, 2
+    n1, n2 = 64, 128                      # global matrix [n1][n2], rank r owns rows r*n1l..
+    n1l, cb = n1 // P, n2 // P
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((n1, n2)) + 1j * rng.standard_normal((n1, n2))
+    recv = [np.zeros(cb * n1, dtype=complex) for _ in range(P)]          # [cb][ld = n1]
+    for r in range(P):
+        mine = x[r * n1l:(r + 1) * n1l]                                   # [rows][cols]
+        rows, cols, ld, row0 = n1l, n2, n1, r * n1l
+        send = np.concatenate([mine[:, j * cb:(j + 1) * cb].T.reshape(-1) for j in range(P)])   # [j][cb][rows]
+        for g in range(G):
+            for j in range(P):
+                doff, dpitch, soff, spitch, width, height = mg.dma_piece_geometry(rows, cols, ld, row0, P, G, g, j)
+                for h in range(height):
+                    recv[j][doff + h * dpitch: doff + h * dpitch + width] = send[soff + h * spitch: soff + h * spitch + width]
+    for j in range(P):
+        assert np.array_equal(recv[j].reshape(cb, n1), x[:, j * cb:(j + 1) * cb].T)

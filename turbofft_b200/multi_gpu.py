@@ -154,6 +154,19 @@ class FourStepFFT:
         return (self.rank * (self.n1 // self.world) + k1_local) + self.n1 * k2
 
 
+def dma_piece_geometry(rows: int, cols: int, ld: int, row0: int, world: int, pieces: int, g: int, j: int):
+    """Element offsets and extents of the 2-D copy that carries piece g of one exchange to receiver j.
+
+    The sender's [rows][cols] matrix is packed per receiver as [cols / world][rows]; receiver j's
+    buffer holds [cols / world] lines of pitch ld and this sender's rows start at row0 in a line.
+    Returns (dst_offset, dst_pitch, src_offset, src_pitch, width, height), offsets and pitches in
+    elements: dst_offset into receiver j's buffer, src_offset into the sender's send buffer.
+    """
+    cb = cols // world
+    piece = cb // pieces
+    return (g * piece * ld + row0, ld, (j * cb + g * piece) * rows, rows, rows, piece)
+
+
 class PeerBuffers:
     """Two receive buffers per rank that every other rank of the node can store into.
 
@@ -338,10 +351,9 @@ class FusedFourStepFFT(FourStepFFT):
             self.copy.wait_event(packed)
             for k in range(1, P):
                 j = (r + k) % P
-                dst = self.bufs.peers[buf][j] + (g * piece * ld + row0) * es
-                srcp = self.send.data_ptr() + (j * cb + g * piece) * rows * es
-                _lib.check(lib().tfft_copy_2d(dst, ld * es, srcp, rows * es, rows * es, piece, self.copy.cuda_stream),
-                           "tfft_copy_2d")
+                doff, dpitch, soff, spitch, width, height = dma_piece_geometry(rows, cols, ld, row0, P, G, g, j)
+                _lib.check(lib().tfft_copy_2d(self.bufs.peers[buf][j] + doff * es, dpitch * es, self.send.data_ptr() + soff * es,
+                                              spitch * es, width * es, height, self.copy.cuda_stream), "tfft_copy_2d")
             sent = torch.cuda.Event()
             sent.record(self.copy)
             self.fence_stream.wait_event(sent)
