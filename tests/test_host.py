@@ -142,6 +142,27 @@ def test_tuner_candidates_are_plannable():
                 assert tune.row_text(r).count(",") == 10
 
 
+def test_tuner_proposes_32_points_per_thread_only_where_it_saves_an_exchange():
+    """E = 32 turns lines of 512 and 1024 points into two register stages instead of three;
+    for other line lengths of a multi-launch split it saves nothing and is not proposed."""
+    from turbofft_b200 import tune
+
+    rows = [r for r in tune.candidates(19, "float2") if r.launches == 2]
+    with32 = [r for r in rows if 32 in r.n[:2]]
+    assert with32
+    for r in with32:
+        for logm, n in zip(r.logni[:2], r.n[:2]):
+            assert n != 32 or logm in (9, 10), tune.row_text(r)
+    assert not [r for r in tune.candidates(19, "double2") if 32 in r.n]   # no registers for it in fp64
+    # the shipped fp32 table uses it for 2^13 and for the long lines of 17..21
+    shipped = planner.load_params("float2", "B200")
+    assert shipped[13].n[0] == 32 and all(32 in shipped[k].n for k in (18, 19, 20))
+    for k in (13, 17, 18, 19, 20, 21):
+        for l in planner.launches_of_row(shipped[k]):
+            if l.loge == 5:
+                assert l.stages == 2 or l.logm >= 13
+
+
 def test_shipped_shared_memory_layouts_are_conflict_free():
     """The generator's bank model on a few shipped instances: the chosen (PADSHIFT, EXTRA)
     reaches the ideal wavefront count, the unpadded layout does not."""
