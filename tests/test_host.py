@@ -169,11 +169,12 @@ def test_shipped_shared_memory_layouts_are_conflict_free():
     from turbofft_b200.codegen import smem_layout as sl
 
     cache = sl.load_cache()
-    for key in ("0_0_12_4_0", "0_1_8_4_4", "0_2_8_4_4", "1_0_12_4_0"):
+    for key in ("0_0_12_4_0", "0_1_8_4_4", "0_2_8_4_4", "1_0_12_4_0", "0_0_13_5_0", "1_0_10_4_0"):
         assert key in cache, key
         f64, role, logm, loge, logc = (int(t) for t in key.split("_"))
-        ps, ex = cache[key]
-        tot, ideal, _ = sl.simulate(role, logm, loge, logc, bool(f64), ps, ex)
+        ps, ex = cache[key][:2]
+        rl = bool(cache[key][2]) if len(cache[key]) > 2 else False
+        tot, ideal, _ = sl.simulate(role, logm, loge, logc, bool(f64), ps, ex, rl)
         assert tot == ideal, (key, tot, ideal)
     tot, ideal, _ = sl.simulate(0, 12, 4, 0, False, sl.NO_PAD, 0)
     assert tot > ideal

@@ -6,7 +6,10 @@ The kernels (csrc/fft_kernels.cuh) place Stockham address a of line c at
 with pad(a) = a + (a >> PADSHIFT) and PITCH = pad(M - 1) + 1 + EXTRA.  This module replays
 every warp-wide shared-memory access of a kernel instance (stage reads, twiddled scatter
 writes, both thread mappings) against the 32 x 4-byte bank model and picks the
-(PADSHIFT, EXTRA) with the fewest wavefronts, smallest footprint first among ties.  The
+(PADSHIFT, EXTRA) with the fewest wavefronts, smallest footprint first among ties.  When the
+line length is not a power of the per-thread radix, the remainder radix normally goes to the
+first stage; if no padded layout is conflict-free that way, the order with the remainder
+radix in the last stage (REMLAST) is searched too.  The
 generator writes the winners to csrc/generated/smem_layouts.h; results are cached in
 smem_layouts.json next to this file because the search takes a while in Python.
 """
@@ -32,7 +35,7 @@ def _wavefronts(addrs, es_words):
     return total, 32 // per
 
 
-def simulate(role, logm, loge, logc, fp64, padshift, extra):
+def simulate(role, logm, loge, logc, fp64, padshift, extra, remlast=False):
     """(wavefronts, ideal wavefronts, elements of shared memory) of one kernel instance."""
     M, E, C = 1 << logm, 1 << loge, 1 << logc
     TPL = M // E
@@ -52,10 +55,14 @@ def simulate(role, logm, loge, logc, fp64, padshift, extra):
 
     tot = ideal = 0
     for st in range(S):
-        LR = LOGR0 if st == 0 else loge
-        LP = 0 if st == 0 else LOGR0 + (st - 1) * loge
-        R, P, NB = 1 << LR, 1 << LP, E >> LR
         last = st == S - 1
+        if remlast:
+            LR = LOGR0 if last else loge
+            LP = st * loge
+        else:
+            LR = LOGR0 if st == 0 else loge
+            LP = 0 if st == 0 else LOGR0 + (st - 1) * loge
+        R, P, NB = 1 << LR, 1 << LP, E >> LR
         cf = (role != 0) if last else (role == 1)
         for w0 in range(0, T, 32):
             tids = list(range(w0, min(w0 + 32, T)))
@@ -98,25 +105,35 @@ def default_layout(role, logm, loge, logc, fp64):
     return ps, ((mpad + bankw - 1) // bankw) * bankw + tpl - mpad
 
 
+def _search(role, logm, loge, logc, fp64, remlast):
+    best = None
+    d = default_layout(role, logm, loge, logc, fp64)
+    cands = [d] + [(ps, ex) for ps in (4, 3, 2, 5, 1, 6, NO_PAD) for ex in (range(0, 17) if role != 1 else [0])]
+    for ps, ex in cands:
+        tot, ideal, elems = simulate(role, logm, loge, logc, fp64, ps, ex, remlast)
+        cand = (tot, elems, ps, ex)
+        if best is None or cand < best:
+            best = cand
+        if tot == ideal and elems <= (1 << logm << logc) * 1.07 + 64:
+            break
+    return best, ideal
+
+
 def best_layout(role, logm, loge, logc, fp64, cache=None):
+    """(PADSHIFT, EXTRA, REMLAST) of one kernel instance."""
     key = f"{int(fp64)}_{role}_{logm}_{loge}_{logc}"
-    if cache is not None and key in cache:
+    if cache is not None and key in cache and len(cache[key]) == 3:
         return tuple(cache[key])
     S = (logm + loge - 1) // loge
     if S < 2:
-        res = default_layout(role, logm, loge, logc, fp64)
+        res = default_layout(role, logm, loge, logc, fp64) + (0,)
     else:
-        best = None
-        d = default_layout(role, logm, loge, logc, fp64)
-        cands = [d] + [(ps, ex) for ps in (4, 3, 2, 5, 1, 6, NO_PAD) for ex in (range(0, 17) if role != 1 else [0])]
-        for ps, ex in cands:
-            tot, ideal, elems = simulate(role, logm, loge, logc, fp64, ps, ex)
-            cand = (tot, elems, ps, ex)
-            if best is None or cand < best:
-                best = cand
-            if tot == ideal and elems <= (1 << logm << logc) * 1.07 + 64:
-                break
-        res = (best[2], best[3])
+        best, ideal = _search(role, logm, loge, logc, fp64, False)
+        res = (best[2], best[3], 0)
+        if best[0] != ideal and logm % loge:
+            alt, ideal = _search(role, logm, loge, logc, fp64, True)
+            if alt[0] < best[0]:
+                res = (alt[2], alt[3], 1)
     if cache is not None:
         cache[key] = list(res)
     return res

@@ -144,15 +144,16 @@ void fill_twiddles(std::vector<C>& v, long long count, long long stride, int log
 // transformed extent P_t = 2^lp, entry (j, b) = W_M^{((b >> lp) << lp) * 2^j} for j < lr and
 // butterfly b < M / R_t.
 template <typename C>
-void stage_twiddles(std::vector<C>& v, int logm, int loge) {
+void stage_twiddles(std::vector<C>& v, int logm, int loge, bool remlast) {
     v.clear();
     const int stages = (logm + loge - 1) / loge;
     const int logr0 = logm - (stages - 1) * loge;
     const long double two_pi = 6.283185307179586476925286766559005768L;
     const long long m = 1LL << logm;
     for (int t = 0; t + 1 < stages; ++t) {
-        const int lr = t == 0 ? logr0 : loge;
-        const int lp = t == 0 ? 0 : logr0 + (t - 1) * loge;
+        // same stage order as Cfg::stage_logr / stage_logp of the kernel
+        const int lr = remlast ? loge : (t == 0 ? logr0 : loge);
+        const int lp = remlast ? t * loge : (t == 0 ? 0 : logr0 + (t - 1) * loge);
         for (int j = 0; j < lr; ++j) {
             const long long q = 1LL << j;
             for (long long b = 0; b < (m >> lr); ++b) {
@@ -215,16 +216,24 @@ bool build_tables(tfft_plan p) {
     typedef typename Cplx<T>::type C;
     for (int i = 0; i < p->n_launch; ++i) {
         LaunchDesc& d = p->L[i];
-        // reuse tables of an earlier launch with the same line length and radix plan
-        int same = -1;
-        for (int j = 0; j < i; ++j)
-            if (p->L[j].logm == d.logm && p->L[j].loge == d.loge) same = j;
+        // reuse tables of an earlier launch with the same line length and radix plan; the stage
+        // twiddles also depend on the stage order, the checksum vector only on the line length
+        int same = -1, same_len = -1;
+        for (int j = 0; j < i; ++j) {
+            if (p->L[j].logm == d.logm) same_len = j;
+            if (p->L[j].logm == d.logm && p->L[j].loge == d.loge && p->L[j].k->remlast == d.k->remlast) same = j;
+        }
         if (same >= 0) {
             d.tw_st = p->L[same].tw_st;
             d.cks = p->L[same].cks;
+        } else if (same_len >= 0 && p->L[same_len].cks) {
+            std::vector<C> t;
+            stage_twiddles(t, d.logm, d.loge, d.k->remlast != 0);
+            if (!upload(p, t, &d.tw_st)) return false;
+            d.cks = p->L[same_len].cks;
         } else {
             std::vector<C> t;
-            stage_twiddles(t, d.logm, d.loge);
+            stage_twiddles(t, d.logm, d.loge, d.k->remlast != 0);
             if (!upload(p, t, &d.tw_st)) return false;
             if (p->if_ft) {
                 std::vector<long double> re, im;
@@ -787,7 +796,7 @@ int static_upload_tables(StaticDeviceState& st, int logN, cudaStream_t stream) {
     for (int i = 0; i < st.n_launch; ++i) {
         LaunchDesc& d = st.L[i];
         std::vector<C> t;
-        stage_twiddles(t, d.logm, d.loge);
+        stage_twiddles(t, d.logm, d.loge, d.k->remlast != 0);
         int rc = place(t, &d.tw_st);
         if (rc != TFFT_OK) return rc;
         if (d.role == ROLE_FIRST) {

@@ -173,7 +173,9 @@ __device__ __forceinline__ void dif_butterfly(C (&v)[E], const int u) {
 
 // ---------------------------------------------------------------- shared-memory layout
 // pad(a) = a + (a >> PADSHIFT); rows layout (ROLE_SINGLE, ROLE_LAST): line pitch =
-// pad(M - 1) + 1 + EXTRA; cols layout (ROLE_FIRST): position pad(a) * C + c.  The primary
+// pad(M - 1) + 1 + EXTRA; cols layout (ROLE_FIRST): position pad(a) * C + c.  REMLAST moves the
+// remainder radix (line length not a power of the per-thread radix) from the first register
+// stage to the last one, for the few instances that have no conflict-free layout otherwise.  The primary
 // template is a reasonable default; generated/smem_layouts.h specialises it per instance
 // with the conflict-free choice found by codegen/smem_layout.py.
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE>
@@ -186,6 +188,7 @@ struct SmemLayout {
     static constexpr int EXTRA = ROLE == ROLE_FIRST ? 0
                                  : ROLE == ROLE_LAST ? ((MPAD | 1) - MPAD)
                                  : (TPL >= BANKW ? 0 : ((MPAD + BANKW - 1) / BANKW) * BANKW + TPL - MPAD);
+    static constexpr int REMLAST = 0;
 };
 #include "generated/smem_layouts.h"
 
@@ -201,12 +204,16 @@ struct Cfg {
     static constexpr int TPL = 1 << LOGTPL;
     static constexpr int THREADS = TPL * C;
     static constexpr int S = (LOGM + LOGE - 1) / LOGE;  // register stages
-    static constexpr int LOGR0 = LOGM - (S - 1) * LOGE; // first stage takes the remainder
+    static constexpr int LOGR0 = LOGM - (S - 1) * LOGE; // the remainder radix: first stage, or last with REMLAST
     static_assert(ROLE != ROLE_LAST || S >= 2, "transposed store needs one exchange");
     static constexpr bool CFAST_IN = (ROLE == ROLE_FIRST);
     static constexpr bool CFAST_OUT = (ROLE != ROLE_SINGLE);
     static constexpr bool LAYOUT_COLS = (ROLE == ROLE_FIRST);
     typedef SmemLayout<T, LOGM, LOGE, LOGC, ROLE> L;
+    static constexpr bool REMLAST = L::REMLAST != 0 && S > 1;
+    // log2 radix of register stage t and log2 of the product of the radices before it
+    static __host__ __device__ constexpr int stage_logr(int t) { return REMLAST ? (t == S - 1 ? LOGR0 : LOGE) : (t == 0 ? LOGR0 : LOGE); }
+    static __host__ __device__ constexpr int stage_logp(int t) { return REMLAST ? t * LOGE : (t == 0 ? 0 : LOGR0 + (t - 1) * LOGE); }
     static constexpr int PADSHIFT = L::PADSHIFT;
     static constexpr int MPAD = (M - 1) + ((M - 1) >> PADSHIFT) + 1;
     static constexpr int PITCH = MPAD + L::EXTRA;
@@ -250,13 +257,13 @@ struct Fft {
         T al[3], be[3];  // fold weights of the right checksum, rotated by s mod 3
     };
 
-    template <int ST> static __device__ __forceinline__ constexpr int logR() { return ST == 0 ? K::LOGR0 : LOGE; }
-    template <int ST> static __device__ __forceinline__ constexpr int logP() { return ST == 0 ? 0 : K::LOGR0 + (ST - 1) * LOGE; }
+    template <int ST> static __device__ __forceinline__ constexpr int logR() { return K::stage_logr(ST); }
+    template <int ST> static __device__ __forceinline__ constexpr int logP() { return K::stage_logp(ST); }
     // first entry of stage ST in the stage-twiddle table: sum over earlier stages of log2(R) * M / R
     template <int ST> static __device__ __forceinline__ constexpr int twOff() {
         int off = 0;
         for (int t = 0; t < ST; ++t) {
-            const int lr = t == 0 ? K::LOGR0 : LOGE;
+            const int lr = K::stage_logr(t);
             off += lr << (LOGM - lr);
         }
         return off;

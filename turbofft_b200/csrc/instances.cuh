@@ -18,7 +18,7 @@
             typedef tfft::Cfg<T, LOGM, LOGE, LOGC, ROLE> K;                                                 \
             tfft::register_kernel(DT, ROLE, LOGM, LOGE, LOGC, FT,                                           \
                                   (const void*)&tfft::fft_kernel<T, LOGM, LOGE, LOGC, ROLE, FT>, K::THREADS, \
-                                  K::smem_bytes(FT));                                                           \
+                                  K::smem_bytes(FT), K::REMLAST ? 1 : 0);                                  \
         }                                                                                                   \
     } TFFT_CAT(tfft_reg_, __LINE__);                                                                        \
     }

@@ -13,10 +13,11 @@ static std::map<Key, KernelEntry>& table() {
 }
 
 void register_kernel(int dtype, int role, int logm, int loge, int logc, int ft, const void* fn, int threads,
-                     size_t smem) {
+                     size_t smem, int remlast) {
     KernelEntry& e = table()[Key(dtype, role, logm, loge, logc)];
     e.fn[ft] = fn;
     e.threads = threads;
+    e.remlast = remlast;
     if (ft == 3) e.smem_csum = smem;
     else e.smem = smem;
 }

@@ -13,10 +13,11 @@ struct KernelEntry {
     int threads;
     size_t smem;        // dynamic shared memory of the first three modes
     size_t smem_csum;   // FT_CSUM adds two tiles of running sums
+    int remlast;        // 1: the remainder radix sits in the last register stage (stage-twiddle table order)
 };
 
 void register_kernel(int dtype, int role, int logm, int loge, int logc, int ft, const void* fn, int threads,
-                     size_t smem);
+                     size_t smem, int remlast);
 const KernelEntry* find_kernel(int dtype, int role, int logm, int loge, int logc);
 int registered_kernel_count();
 // counts one kernel launch of this library (see tfft_launch_count)
