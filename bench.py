@@ -447,7 +447,7 @@ def run_ours(a):
         "per_point": per_point,
     }
     cpu = None
-    if not a.no_cpu:
+    if not a.no_cpu and world == 1:  # the host baseline is a single-GPU-run figure; rank 0 of a larger job skips it
         cpu_sweep(a)  # warms the thread pool and the allocator
         gf, t, workers, ls, _ = cpu_sweep(a, grow=2)
         cpu = {"value": gf, "unit": "GFLOPS", "cores": workers, "kind": "port",
