@@ -175,7 +175,8 @@ __device__ __forceinline__ void dif_butterfly(C (&v)[E], const int u) {
 // pad(a) = a + (a >> PADSHIFT); rows layout (ROLE_SINGLE, ROLE_LAST): line pitch =
 // pad(M - 1) + 1 + EXTRA; cols layout (ROLE_FIRST): position pad(a) * C + c.  REMLAST moves the
 // remainder radix (line length not a power of the per-thread radix) from the first register
-// stage to the last one, for the few instances that have no conflict-free layout otherwise.  The primary
+// stage to the last one; the generator picks it wherever that order is at least as free of
+// bank conflicts (for a few instances it is the only conflict-free one).  The primary
 // template is a reasonable default; generated/smem_layouts.h specialises it per instance
 // with the conflict-free choice found by codegen/smem_layout.py.
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE>
