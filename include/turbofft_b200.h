@@ -55,7 +55,7 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
  * batch*N complex elements; the result is always at `out` (the reference leaves
  * it in a launch-count dependent half of a 2x buffer, main.cu:11-12,72).
  * in == out is allowed except for 1-launch plans with if_err (the located tile
- * is recomputed from the input).  `stream` is a cudaStream_t (NULL = default).
+ * is recomputed from the input; see tfft_set_correction for the way around).  `stream` is a cudaStream_t (NULL = default).
  * Stream ordered; returns without synchronising. */
 int tfft_exec(tfft_plan plan, const void* in, void* out, void* stream);
 
@@ -90,8 +90,10 @@ int tfft_set_ft_params(tfft_plan plan, double err_inj, double err_smoothing, dou
  * prepares (it accumulates both sums, fft_codegen.py:356-357,422-423) but leaves commented
  * out (:370,:403,:427-429; test.ipynb cell 0).  It does not read the input again, so a
  * 1-launch plan may then run in place; it costs two more tiles of shared memory per block.
- * Available for single and last launches (first/middle launches keep recomputing, their
- * input is never overwritten); TFFT_ERR_UNSUPPORTED if no launch of the plan has it.
+ * Available for single and last launches; first and middle launches keep recomputing, and
+ * no launch of a correcting plan overwrites what it reads (a three-launch plan created with
+ * if_err owns a second scratch buffer for its middle launch, as the reference alternates
+ * two buffers, main.cu:11-12).  TFFT_ERR_UNSUPPORTED if no launch of the plan has it.
  * The repaired outputs equal the fault-free ones up to rounding, not bit for bit. */
 int tfft_set_correction(tfft_plan plan, int from_checksums);
 
@@ -120,6 +122,14 @@ int tfft_set_injection(tfft_plan plan, int enable, int launch, int period, int p
 int tfft_ft_status(tfft_plan plan, int* n_detected, int* n_corrected, int launch, int* located, int cap,
                    int* n_blocks);
 
+/* Counter mode (no counterpart in the reference, whose kernels keep no counters).  0
+ * (default): n_detected / n_corrected describe the most recent tfft_exec.  1: they add up
+ * over every tfft_exec until tfft_ft_status reads them, which also clears them -- for
+ * callers that run one plan many times per job (the pieces of a pipelined multi-GPU
+ * transform) and want the job's totals.  The per-block `located` array is always the last
+ * exec's. */
+int tfft_set_ft_accumulate(tfft_plan plan, int enable);
+
 /* Per-block checksum residuals of launch `launch` from the most recent exec:
  * delta, S, delta_w as doubles, 3 per block (fft_codegen.py:432-495 keeps them
  * in registers).  Only recorded after tfft_enable_ft_diag(plan, 1). */
@@ -132,15 +142,22 @@ int tfft_plan_destroy(tfft_plan plan);
  * device memory when they call (no cudaMalloc allowed: pool-managed regions, allocation-free
  * service loops, devices whose memory is fully handed out).  Runs the built-in multi-launch
  * plan for (logN, dtype), FT off, with the intermediate buffer and the twiddle tables in
- * static device arrays of the library (16 MiB + 512 KiB held by every GPU that loads it).
- * Limits: the size must be a multi-launch one of the built-in table (currently logN >= 15
- * float2, >= 14 double2; at most 24) and
- * batch * 2^logN * sizeof(element) <= 16 MiB, else TFFT_ERR_UNSUPPORTED / TFFT_ERR_TOO_LARGE.
- * Calls no cudaMalloc/cudaFree.  The first call on a device looks up the arrays' device
- * addresses; make that call before any stream capture.  All calls share the arrays, which
- * keep the previous call's contents (every element that is read is written first, so
- * nothing needs clearing); two calls whose kernels overlap on the GPU race -- issue them
- * on one stream or synchronise in between. */
+ * static device arrays of the library (16 MiB + 512 KiB per GPU that uses it).
+ * Limits: the size must be a multi-launch one of the built-in table (tfft_plan_info tells;
+ * at most logN 24) and batch * 2^logN * sizeof(element) <= 16 MiB, else
+ * TFFT_ERR_UNSUPPORTED / TFFT_ERR_TOO_LARGE.  Calls no cudaMalloc/cudaFree.
+ * Set-up: the first call on a device looks up the arrays' device addresses.  With CUDA's
+ * lazy module loading (the default) that look-up, and the first launch of each kernel, is
+ * also the moment the driver reserves the arrays and loads the code, so make one warm-up
+ * call per device and size BEFORE entering the region that must not allocate and before
+ * any stream capture (or run with CUDA_MODULE_LOADING=EAGER).
+ * Tables: the twiddle tables of the last (logN, dtype) stay in the static table array.  A
+ * call with the same (logN, dtype) reuses them and issues kernels only; a call with another
+ * size rebuilds them on the host and uploads them on the caller's stream from pageable
+ * memory, which a stream capture cannot record -- so only repeat sizes inside a capture.
+ * Sharing: all calls share the arrays, which keep the previous call's contents (every
+ * element that is read is written first, so nothing needs clearing); two calls whose
+ * kernels overlap on the GPU race -- issue them on one stream or synchronise in between. */
 int tfft_exec_static(int logN, long long batch, int dtype, const void* in, void* out, int device, void* stream);
 
 /* Last CUDA error code seen by any call on this plan (0 = none). */

@@ -147,6 +147,36 @@ def test_sparse_injection_in_either_launch(torch_cuda, dtype, launch):
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("tbs", [2, 8])
+@pytest.mark.parametrize("launch", [0, 1, 2])
+def test_three_launch_plan_corrects_in_every_launch(torch_cuda, dtype, tbs, launch):
+    """A three-launch plan with faults in its first, middle or last launch: the located
+    indices are the injected ones and the repaired output equals the fault-free run bit for
+    bit, out of place and in place.  The middle launch is the one whose input would be gone
+    if it ran in place in the scratch buffer; the reference alternates two buffers
+    (main.cu:11-12) and recomputes from the launch's input (fft_codegen.py:149-193)."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    logn, batch, period, phase = 23, 1, 5, 2
+    assert len(planner.launches_of_row(planner.load_params(DT[dtype])[logn])) == 3
+    x = (orc.make_input(batch, 1 << logn, CD[dtype], seed=23) * 0.01).astype(CD[dtype])
+    _, y0 = _run(torch, logn, batch, dtype, x)
+    plan = tf.Plan(logn, batch, dtype, if_ft=1, if_err=1, thread_bs=tbs)
+    plan.set_injection(True, launch=launch, period=period, phase=phase)
+    for inplace in (False, True):
+        xd = torch.from_numpy(x).cuda()
+        y = plan(xd, out=xd if inplace else None).cpu().numpy()
+        nd, nc, loc = plan.ft_status(launch)
+        expect = [orc.injected_tile_iteration(b, tbs, period) if b % period == phase else -1 for b in range(len(loc))]
+        assert loc == expect
+        for other in {0, 1, 2} - {launch}:
+            assert all(k == -1 for k in plan.ft_status(other)[2])
+        assert nd == nc == sum(k != -1 for k in expect) > 0
+        assert np.array_equal(y, y0), (launch, inplace)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
 @pytest.mark.parametrize("logn,tbs", [(10, 4), (12, 2), (8, 8)])
 def test_decisions_match_cpu_model(torch_cuda, logn, tbs, dtype):
     """Per block (delta, S, delta_w) from the kernel against the CPU restatement of the

@@ -39,8 +39,11 @@ def test_fft_matches_oracle(torch_cuda, logn, dtype):
     _, y = run_plan(torch_cuda, logn, batch, dtype, x)
     err = orc.rel_l2(y, orc.fft_forward(x))
     assert err <= orc.tolerance(CD[dtype], logn), (logn, dtype, err)
-    ok, idx, comp = orc.compare_data(y, orc.fft_forward(x).astype(CD[dtype]), 1e-4 * max(1, 1 << max(0, logn - 10)) if dtype == 0 else 1e-4)
-    assert ok or dtype == 0, (idx, comp)
+    # the reference's own acceptance test (compareData.h:4-35, bound 1e-4 per component at its
+    # 2^10 verify case); for complex64 the bound grows with the output magnitude beyond 2^10
+    bound = 1e-4 * max(1, 1 << max(0, logn - 10)) if dtype == 0 else 1e-4
+    ok, idx, comp = orc.compare_data(y, orc.fft_forward(x).astype(CD[dtype]), bound)
+    assert ok, (idx, comp)
 
 
 @pytest.mark.parametrize("dtype", [0, 1])

@@ -110,6 +110,10 @@ class Plan:
     def set_injection(self, enable: bool = True, launch: int = -1, period: int = 1, phase: int = 0):
         _lib.check(lib().tfft_set_injection(self._h, int(enable), launch, period, phase), "tfft_set_injection")
 
+    def set_ft_accumulate(self, enable: bool = True):
+        """FT counters add up over calls until ft_status() reads (and clears) them."""
+        _lib.check(lib().tfft_set_ft_accumulate(self._h, int(enable)), "tfft_set_ft_accumulate")
+
     def enable_ft_diag(self, enable: bool = True):
         _lib.check(lib().tfft_enable_ft_diag(self._h, int(enable)), "tfft_enable_ft_diag")
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "tfft_ft_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int),
                                  C.c_int, C.POINTER(C.c_int)]),
     "tfft_enable_ft_diag": (C.c_int, [C.c_void_p, C.c_int]),
+    "tfft_set_ft_accumulate": (C.c_int, [C.c_void_p, C.c_int]),
     "tfft_ft_diag": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.c_int]),
     "tfft_plan_destroy": (C.c_int, [C.c_void_p]),
     "tfft_exec_static": (C.c_int, [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

@@ -81,6 +81,8 @@ struct tfft_plan_s {
     int n_launch = 0;
     LaunchDesc L[3];
     void* scratch = nullptr;
+    void* scratch2 = nullptr;          // 3-launch plans that correct: the middle launch writes here, so that
+                                       // its own input survives for the recompute of a located tile
     unsigned int* ft_count = nullptr;  // [3][2]
     size_t owned_bytes = 0;
     double err_inj = TFFT_DEFAULT_ERR_INJ;
@@ -88,6 +90,7 @@ struct tfft_plan_s {
     double err_threshold = TFFT_DEFAULT_ERR_THRESHOLD;
     int inj_enable = 0, inj_launch = -1, inj_period = 1, inj_phase = 0;
     int diag = 0;
+    int ft_accumulate = 0;  // 1: the FT counters add up over execs until tfft_ft_status reads (and clears) them
     int csum = 0;        // 1: repair from the running checksums (FT_CSUM kernels) where they exist
     int inverse = 0;     // 0: forward; 1: conjugate in, conjugate out (inverse transform)
     double scale = 1.0;  // applied with the conjugation of the last launch
@@ -272,7 +275,7 @@ template <typename T>
 int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
     typedef typename Cplx<T>::type C;
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
-    if (p->if_ft) {
+    if (p->if_ft && !p->ft_accumulate) {
         if (!cuda_ok(p, cudaMemsetAsync(p->ft_count, 0, 6 * sizeof(unsigned int), st))) return TFFT_ERR_CUDA;
     }
     const int inj_launch = p->inj_launch < 0 ? p->n_launch - 1 : p->inj_launch;
@@ -280,8 +283,13 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         const LaunchDesc& d = p->L[i];
         KernelArgs<T> a;
         memset(&a, 0, sizeof(a));
-        a.in = (const C*)(i == 0 ? in : p->scratch);
-        a.out = (C*)(i == p->n_launch - 1 ? out : p->scratch);
+        // Buffers.  Plain plans: launch 0 in -> scratch, a middle launch in place in scratch, last
+        // launch scratch -> out.  A correcting plan recomputes a located tile from the launch's
+        // input, so no launch may overwrite what it reads: its middle launch goes scratch ->
+        // scratch2 (the reference alternates two buffers for every launch, main.cu:11-12).
+        const bool pingpong = p->scratch2 != nullptr;
+        a.in = (const C*)(i == 0 ? in : (i == 2 && pingpong ? p->scratch2 : p->scratch));
+        a.out = (C*)(i == p->n_launch - 1 ? out : (i == 1 && pingpong ? p->scratch2 : p->scratch));
         a.tw_st = (const C*)d.tw_st;
         a.tw_lo = (const C*)d.tw_lo;
         a.tw_hi = (const C*)d.tw_hi;
@@ -407,6 +415,10 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
     if (status == TFFT_OK && p->n_launch > 1) {
         p->scratch = dev_alloc(p, ((size_t)batch << logN) * p->esize());
         if (!p->scratch) status = TFFT_ERR_ALLOC;
+        if (status == TFFT_OK && p->n_launch == 3 && p->if_err) {
+            p->scratch2 = dev_alloc(p, ((size_t)batch << logN) * p->esize());
+            if (!p->scratch2) status = TFFT_ERR_ALLOC;
+        }
     }
     if (status == TFFT_OK && p->if_ft) {
         p->ft_count = (unsigned int*)dev_alloc(p, 6 * sizeof(unsigned int));
@@ -633,6 +645,7 @@ int tfft_ft_status(tfft_plan p, int* n_detected, int* n_corrected, int launch, i
     if (!cuda_ok(p, cudaStreamSynchronize(p->last_stream))) return TFFT_ERR_CUDA;
     unsigned int cnt[6];
     if (!cuda_ok(p, cudaMemcpy(cnt, p->ft_count, sizeof(cnt), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
+    if (p->ft_accumulate && !cuda_ok(p, cudaMemset(p->ft_count, 0, sizeof(cnt)))) return TFFT_ERR_CUDA;
     for (int i = 0; i < p->n_launch; ++i) {
         if (n_detected) *n_detected += (int)cnt[2 * i];
         if (n_corrected) *n_corrected += (int)cnt[2 * i + 1];
@@ -645,6 +658,12 @@ int tfft_ft_status(tfft_plan p, int* n_detected, int* n_corrected, int launch, i
         if (!cuda_ok(p, cudaMemcpy(located, p->L[launch].ft_located, n * sizeof(int), cudaMemcpyDeviceToHost)))
             return TFFT_ERR_CUDA;
     }
+    return TFFT_OK;
+}
+
+int tfft_set_ft_accumulate(tfft_plan p, int enable) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    p->ft_accumulate = enable ? 1 : 0;
     return TFFT_OK;
 }
 
@@ -778,38 +797,64 @@ int static_geometry(const ParamRow& row, int logN, long long batch, int dtype, L
     return TFFT_OK;
 }
 
-// Builds the twiddle tables of the launches on the host and copies them into the static
-// table region (stream ordered).  No allocation on the device.
+// Number of entries of stage_twiddles(logm, loge, *): sum over all stages but the last of
+// log2(R_t) * M / R_t; the set of radices does not depend on the stage order.
+size_t stage_twiddle_count(int logm, int loge) {
+    const int stages = (logm + loge - 1) / loge;
+    const int logr0 = logm - (stages - 1) * loge;
+    if (stages == 1) return 1;
+    // remainder radix first: stages 0..S-2 = logr0, loge, ...; remainder last: loge x (S-1).
+    // The kernel reads the table in its own order, so both cases are sized for the larger one.
+    size_t first = (size_t)logr0 << (logm - logr0), last = 0;
+    for (int t = 1; t + 1 < stages; ++t) first += (size_t)loge << (logm - loge);
+    for (int t = 0; t + 1 < stages; ++t) last += (size_t)loge << (logm - loge);
+    return first > last ? first : last;
+}
+
+// Lays the twiddle tables of the launches out in the static table region and, if `fill`,
+// builds them on the host and copies them there (stream ordered).  The layout depends only
+// on (logN, dtype), so a call that finds its own tables already resident passes fill = false
+// and only gets the pointers.  No allocation on the device.
 template <typename T>
-int static_upload_tables(StaticDeviceState& st, int logN, cudaStream_t stream) {
+int static_place_tables(StaticDeviceState& st, bool fill, cudaStream_t stream) {
     typedef typename Cplx<T>::type C;
     size_t off = 0;
-    auto place = [&](const std::vector<C>& host, void** dev) -> int {
-        const size_t bytes = host.size() * sizeof(C);
+    auto reserve = [&](size_t count, void** dev) -> int {
+        const size_t bytes = count * sizeof(C);
         if (off + bytes > kStaticTableBytes) return TFFT_ERR_TOO_LARGE;
         *dev = (unsigned char*)st.tables + off;
-        // pageable source: the call returns once the data is staged, so `host` may go away
-        if (cudaMemcpyAsync(*dev, host.data(), bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return TFFT_ERR_CUDA;
         off += (bytes + 255) & ~(size_t)255;
         return TFFT_OK;
     };
+    auto copy = [&](const std::vector<C>& host, void* dev) -> int {
+        // pageable source: cudaMemcpyAsync returns once the data is staged, so `host` may go away
+        return cudaMemcpyAsync(dev, host.data(), host.size() * sizeof(C), cudaMemcpyHostToDevice, stream) == cudaSuccess
+                   ? TFFT_OK
+                   : TFFT_ERR_CUDA;
+    };
     for (int i = 0; i < st.n_launch; ++i) {
         LaunchDesc& d = st.L[i];
-        std::vector<C> t;
-        stage_twiddles(t, d.logm, d.loge, d.k->remlast != 0);
-        int rc = place(t, &d.tw_st);
+        int rc = reserve(stage_twiddle_count(d.logm, d.loge), &d.tw_st);
         if (rc != TFFT_OK) return rc;
+        if (fill) {
+            std::vector<C> t;
+            stage_twiddles(t, d.logm, d.loge, d.k->remlast != 0);
+            if ((rc = copy(t, d.tw_st)) != TFFT_OK) return rc;
+        }
         if (d.role == ROLE_FIRST) {
             const int logp = d.logm + d.log_b;
             d.tw_lo_bits = (logp + 1) / 2;
-            std::vector<C> lo, hi;
-            fill_twiddles(lo, 1LL << d.tw_lo_bits, 1, logp);
-            fill_twiddles(hi, 1LL << (logp - d.tw_lo_bits), 1LL << d.tw_lo_bits, logp);
-            if ((rc = place(lo, &d.tw_lo)) != TFFT_OK) return rc;
-            if ((rc = place(hi, &d.tw_hi)) != TFFT_OK) return rc;
+            if ((rc = reserve((size_t)1 << d.tw_lo_bits, &d.tw_lo)) != TFFT_OK) return rc;
+            if ((rc = reserve((size_t)1 << (logp - d.tw_lo_bits), &d.tw_hi)) != TFFT_OK) return rc;
+            if (fill) {
+                std::vector<C> lo, hi;
+                fill_twiddles(lo, 1LL << d.tw_lo_bits, 1, logp);
+                fill_twiddles(hi, 1LL << (logp - d.tw_lo_bits), 1LL << d.tw_lo_bits, logp);
+                if ((rc = copy(lo, d.tw_lo)) != TFFT_OK) return rc;
+                if ((rc = copy(hi, d.tw_hi)) != TFFT_OK) return rc;
+            }
         }
     }
-    (void)logN;
     return TFFT_OK;
 }
 
@@ -850,7 +895,7 @@ extern "C" int tfft_exec_static(int logN, long long batch, int dtype, const void
         return TFFT_ERR_BAD_ARG;
     const size_t esize = dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2);
     // the whole intermediate result must fit in the static scratch array
-    if (((unsigned long long)batch << logN) > kStaticScratchBytes / esize) return TFFT_ERR_TOO_LARGE;
+    if ((unsigned long long)batch > ((kStaticScratchBytes / esize) >> logN)) return TFFT_ERR_TOO_LARGE;
     std::vector<ParamRow> rows;
     std::string err;
     if (!parse_param_csv(builtin_param_csv(dtype), rows, err)) return TFFT_ERR_PARAM_FILE;
@@ -876,9 +921,14 @@ extern "C" int tfft_exec_static(int logN, long long batch, int dtype, const void
             cudaFuncSetAttribute(st.L[i].k->fn[FT_OFF], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st.L[i].k->smem) !=
                 cudaSuccess)
             return TFFT_ERR_CUDA;
-    // (re)fill the table region; it keeps the previous call's tables, so a call with the same
-    // (logN, dtype) could skip this, but the table pointers are recomputed either way
-    rc = dtype == TFFT_FLOAT2 ? static_upload_tables<float>(st, logN, s) : static_upload_tables<double>(st, logN, s);
+    // The table region keeps the previous call's tables: a call with the same (logN, dtype)
+    // finds them in place and only recomputes the pointers -- no host table building and no
+    // host-to-device copy, which is what a call inside a stream capture needs.  A change of
+    // size rebuilds them on the host and uploads them on the caller's stream, behind the
+    // previous call's kernels.
+    const bool fill = !(st.table_logn == logN && st.table_dtype == dtype);
+    if (fill) st.table_logn = st.table_dtype = -1;  // nothing valid if the upload fails half way
+    rc = dtype == TFFT_FLOAT2 ? static_place_tables<float>(st, fill, s) : static_place_tables<double>(st, fill, s);
     if (rc != TFFT_OK) return rc;
     st.table_logn = logN;
     st.table_dtype = dtype;

@@ -298,6 +298,7 @@ class FusedFourStepFFT(FourStepFFT):
         key = (logn, count)
         if key not in self._plans:
             self._plans[key] = Plan(logn, count, self.dt, self.be.if_ft, self.be.if_err, self.be.thread_bs, device=self.dev)
+            self._plans[key].set_ft_accumulate(True)
         return self._plans[key]
 
     def _exchange_and_transform(self, src, buf, rows, cols, ld, row0, tw, line_log, lines, out):
@@ -374,12 +375,7 @@ class FusedFourStepFFT(FourStepFFT):
         return out
 
     def _fft_from(self, src_ptr, logn, count, out):
-        from . import Plan
-
-        key = (logn, count)
-        if key not in self._plans:
-            self._plans[key] = Plan(logn, count, self.dt, self.be.if_ft, self.be.if_err, self.be.thread_bs, device=self.dev)
-        self._plans[key].exec_ptr(src_ptr, out.data_ptr(), self._stream())
+        self._plan(logn, count).exec_ptr(src_ptr, out.data_ptr(), self._stream())
         return out
 
     def __call__(self, x_local):
@@ -403,6 +399,7 @@ class FusedFourStepFFT(FourStepFFT):
             res = self.torch.empty_like(x_local)
             _lib.check(lib().tfft_stream_copy(self.bufs.local[0], res.data_ptr(), res.numel() * self.esize, self._stream()),
                        "tfft_stream_copy")
+            self._fence()   # see the end of this method
             return res
         # 1. x[n1l][N2] -> every rank's buffer 0 as [n2l][N1]
         self._scatter(x_local.data_ptr(), 0, n1l, n2, n1, r * n1l, False)
@@ -422,9 +419,16 @@ class FusedFourStepFFT(FourStepFFT):
         # device-to-device copy of this rank's slab out of the receive buffer (stream ordered)
         _lib.check(lib().tfft_stream_copy(self.bufs.local[0], res.data_ptr(), res.numel() * self.esize, self._stream()),
                    "tfft_stream_copy")
+        # The copy reads receive buffer 0, which the NEXT call's first exchange overwrites from
+        # every peer.  Without a barrier here a faster peer's stores could land while this rank
+        # still copies out (write after read across GPUs), so all ranks meet once more.
+        self._fence()
         return res
 
     def ft_counts(self):
+        """(detected, corrected) summed over every local transform since the last call of this
+        method: the plans run once per pipeline piece and per pass, so they accumulate their
+        counters (tfft_set_ft_accumulate) instead of keeping only the last run's."""
         nd = nc = 0
         for p in self._plans.values():
             d, c, _ = p.ft_status()
