@@ -50,6 +50,22 @@ enum { TFFT_FLOAT2 = 0, TFFT_DOUBLE2 = 1 };
 int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int if_ft, int if_err,
                      int thread_bs, const char* param_csv, int device);
 
+/* No counterpart in the reference, whose plans for 2^13..2^17 points are two launches
+ * through a scratch buffer (include/param/A100/param_float2.csv rows 13-17).  Single-pass
+ * plan: the whole signal is held in the shared memory of a thread-block cluster of
+ * 2^log_cluster CTAs (distributed shared memory for the one exchange that crosses CTAs), so
+ * HBM is read once and written once and the plan owns no scratch buffer.  log_cluster = -1
+ * picks the default cluster size of the size.  FT off only; thread_bs = signals per cluster.
+ * TFFT_ERR_UNSUPPORTED if no such kernel exists for (logN, dtype, log_cluster) or the device
+ * cannot hold one cluster of it.  tfft_plan_create() makes this kind of plan by itself for
+ * the sizes of the built-in single-pass table (param/B200/single_pass_<dtype>.csv) when
+ * if_ft == 0 and param_csv == NULL.  `in` must be aligned to the element size and `out` to
+ * 16 bytes; in == out is allowed. */
+int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int dtype, int log_cluster,
+                                 int thread_bs, int device);
+/* CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches. */
+int tfft_plan_cluster_size(tfft_plan plan);
+
 /* Replaces: the launch loop of test_turbofft() (main.cu:53-62) without its
  * per-launch cudaDeviceSynchronize().  `in` and `out` are device pointers to
  * batch*N complex elements; the result is always at `out` (the reference leaves

@@ -1,0 +1,86 @@
+"""Single-pass plans (one thread-block-cluster kernel, distributed shared memory exchange)
+against the CPU oracle, through the C ABI (tfft_plan_create_single_pass).
+
+Same tolerances as the multi-launch plans: relative L2 <= 1e-6 * log2 N (complex64) and
+<= 1e-14 * log2 N (complex128) against the float64 oracle.  The reference has no such
+kernel: its plans for these sizes are two launches (include/param/A100/param_float2.csv
+rows 13-17), so the comparison partner besides the oracle is this library's own
+multi-launch plan for the same size.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import fft_oracle as orc
+
+pytestmark = pytest.mark.gpu
+CD = {0: np.complex64, 1: np.complex128}
+
+# (dtype, logN, log2 cluster sizes compiled for it)
+SIZES = [(0, 13, (0, 1)), (0, 14, (1, 2, 0)), (0, 15, (3, 2, 1)), (0, 16, (4, 3, 2)), (0, 17, (4, 3)),
+         (1, 12, (0,)), (1, 13, (1,)), (1, 14, (2,)), (1, 15, (3,)), (1, 16, (4, 3))]
+CASES = [(dt, logn, g) for dt, logn, gs in SIZES for g in gs]
+
+
+@pytest.mark.parametrize("dtype,logn,log_cluster", CASES)
+def test_single_pass_matches_oracle(torch_cuda, dtype, logn, log_cluster):
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    for batch, tbs in ((5, 2), (1, 1), (7, 3)):     # ragged: the last cluster runs out of signals
+        x = orc.make_input(batch, 1 << logn, CD[dtype], seed=logn + batch)
+        plan = tf.Plan(logn, batch, dtype, single_pass=log_cluster, thread_bs=tbs)
+        assert plan.cluster_size == 1 << log_cluster and len(plan.info()) == 1
+        xd = torch.from_numpy(x).cuda()
+        y = plan(xd)
+        torch.cuda.synchronize()
+        assert torch.equal(xd.cpu(), torch.from_numpy(x))              # input untouched
+        err = orc.rel_l2(y.cpu().numpy(), orc.fft_forward(x))
+        assert err <= orc.tolerance(CD[dtype], logn), (logn, log_cluster, batch, err)
+        y2 = plan(xd, out=xd)                                          # in place
+        torch.cuda.synchronize()
+        assert torch.equal(y, y2)
+        plan.destroy()
+
+
+@pytest.mark.parametrize("dtype,logn", [(0, 15), (1, 14)])
+def test_single_pass_agrees_with_the_launches(torch_cuda, dtype, logn):
+    """Default cluster size (-1) against the multi-launch plan of the same size, and the
+    inverse transform with 1/N scaling brings the signal back."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    batch = 6
+    x = orc.make_input(batch, 1 << logn, CD[dtype], seed=3)
+    xd = torch.from_numpy(x).cuda()
+    csv = os.path.join(os.path.dirname(tf.__file__), "param", "B200", "param_float2.csv" if dtype == 0 else "param_double2.csv")
+    y_launches = tf.Plan(logn, batch, dtype, param_csv=csv)(xd)
+    sp = tf.Plan(logn, batch, dtype, single_pass=-1)
+    y = sp(xd)
+    scale = float(torch.linalg.vector_norm(y_launches))
+    assert float(torch.linalg.vector_norm(y - y_launches)) / scale <= orc.tolerance(CD[dtype], logn)
+    lib = tf.lib()
+    assert lib.tfft_set_direction(sp._h, 1, 1.0 / (1 << logn)) == 0
+    back = sp(y)
+    torch.cuda.synchronize()
+    assert orc.rel_l2(back.cpu().numpy(), x) <= 2 * orc.tolerance(CD[dtype], logn)
+
+
+def test_single_pass_refuses_what_it_cannot_do(torch_cuda):
+    import ctypes as C
+
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    lib = tf.lib()
+    h = C.c_void_p()
+    assert lib.tfft_plan_create_single_pass(C.byref(h), 10, 4, 0, -1, 1, 0) == -2     # no such kernel
+    assert lib.tfft_plan_create_single_pass(C.byref(h), 15, 4, 0, 7, 1, 0) == -2      # no such cluster size
+    assert lib.tfft_plan_create_single_pass(C.byref(h), 15, 0, 0, -1, 1, 0) == -1     # bad batch
+    plan = tf.Plan(15, 2, 0, single_pass=-1)
+    buf = torch.zeros((2 << 15) + 1, dtype=torch.complex64, device="cuda")
+    x = torch.zeros(2 << 15, dtype=torch.complex64, device="cuda")
+    # an output that is only 8-byte aligned is refused, not silently mis-stored
+    rc = lib.tfft_exec(plan._h, x.data_ptr(), buf.data_ptr() + 8, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1

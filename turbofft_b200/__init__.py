@@ -38,13 +38,26 @@ class Plan:
     """One (logN, batch, dtype, FT mode) plan on one device."""
 
     def __init__(self, logN: int, batch: int, dtype: int = FLOAT2, if_ft: int = 0, if_err: int = 0,
-                 thread_bs: int = 1, param_csv: Optional[str] = None, device: int = 0):
+                 thread_bs: int = 1, param_csv: Optional[str] = None, device: int = 0,
+                 single_pass: Optional[int] = None):
+        """single_pass = g asks for the one-kernel cluster plan with 2^g CTAs per cluster (-1 = the
+        size's default); None lets tfft_plan_create choose (built-in tables)."""
         self._h = C.c_void_p()
         self.logN, self.batch, self.dtype = int(logN), int(batch), int(dtype)
         self.if_ft, self.if_err, self.thread_bs, self.device = int(bool(if_ft or if_err)), int(if_err), int(thread_bs), int(device)
+        if single_pass is not None:
+            rc = lib().tfft_plan_create_single_pass(C.byref(self._h), self.logN, self.batch, self.dtype, int(single_pass),
+                                                    self.thread_bs, self.device)
+            _lib.check(rc, f"tfft_plan_create_single_pass(logN={logN}, batch={batch}, dtype={dtype}, log_cluster={single_pass})")
+            return
         rc = lib().tfft_plan_create(C.byref(self._h), self.logN, self.batch, self.dtype, int(if_ft), int(if_err),
                                     self.thread_bs, param_csv.encode() if param_csv else None, self.device)
         _lib.check(rc, f"tfft_plan_create(logN={logN}, batch={batch}, dtype={dtype}, ft={if_ft}, err={if_err})")
+
+    @property
+    def cluster_size(self) -> int:
+        """CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches."""
+        return lib().tfft_plan_cluster_size(self._h)
 
     # -- execution
     def exec_ptr(self, in_ptr: int, out_ptr: int, stream: int = 0) -> None:

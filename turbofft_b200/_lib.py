@@ -21,6 +21,8 @@ STATUS = {
 SIGNATURES = {
     "tfft_plan_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_char_p, C.c_int]),
+    "tfft_plan_create_single_pass": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "tfft_plan_cluster_size": (C.c_int, [C.c_void_p]),
     "tfft_exec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tfft_exec_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tfft_workspace_bytes": (C.c_size_t, [C.c_void_p]),

@@ -8,6 +8,7 @@
 #include <map>
 #include <mutex>
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -18,6 +19,7 @@
 #include "generated/ft_defaults.h"
 #include "params.h"
 #include "registry.h"
+#include "cluster_registry.h"
 
 using namespace tfft;
 
@@ -80,6 +82,11 @@ struct tfft_plan_s {
     int dtype = 0, if_ft = 0, if_err = 0, thread_bs = 1, device = 0;
     int n_launch = 0;
     LaunchDesc L[3];
+    // single-pass plan (one cluster kernel, no scratch): kernel, its tables, signals per cluster
+    const ClusterKernel* ck = nullptr;
+    void* ctw0 = nullptr;
+    void* ctwp[4] = {nullptr, nullptr, nullptr, nullptr};
+    unsigned cgrid_clusters = 0;
     void* scratch = nullptr;
     void* scratch2 = nullptr;          // 3-launch plans that correct: the middle launch writes here, so that
                                        // its own input survives for the recompute of a located tile
@@ -262,6 +269,16 @@ bool build_tables(tfft_plan p) {
     return true;
 }
 
+template <typename T>
+bool build_cluster_tables(tfft_plan p) {
+    std::vector<T> tw0, twp[4];
+    cluster_twiddles<T>(*p->ck, tw0, twp);
+    if (!upload(p, tw0, &p->ctw0)) return false;
+    for (int t = 0; t + 1 < p->ck->s2; ++t)
+        if (!upload(p, twp[t], &p->ctwp[t])) return false;
+    return true;
+}
+
 int ilog2_exact(long long x) {
     int l = 0;
     while ((1LL << l) < x) ++l;
@@ -272,8 +289,31 @@ int ilog2_exact(long long x) {
 bool csum_ok(const KernelEntry* k) { return k && k->fn[FT_CSUM] && k->smem_csum <= 227u * 1024u; }
 
 template <typename T>
+int launch_cluster(tfft_plan p, const void* in, void* out, cudaStream_t st) {
+    typedef typename Cplx<T>::type C;
+    // the kernel stores 16 bytes per lane
+    if (((uintptr_t)out & 15u) || ((uintptr_t)in & (sizeof(C) - 1))) return TFFT_ERR_BAD_ARG;
+    ClusterArgs<T> a;
+    memset(&a, 0, sizeof(a));
+    a.in = (const C*)in;
+    a.out = (C*)out;
+    a.tw0 = (const C*)p->ctw0;
+    for (int t = 0; t < 4; ++t) a.twp[t] = (const T*)p->ctwp[t];
+    a.n_signals = p->batch;
+    a.signals_per_cluster = p->thread_bs;
+    a.conj_in = p->inverse ? 1 : 0;
+    a.scale_out = (p->inverse || p->scale != 1.0) ? 1 : 0;
+    a.scale_x = (T)p->scale;
+    a.scale_y = (T)(p->inverse ? -p->scale : p->scale);
+    if (!cuda_ok(p, launch_cluster_kernel(*p->ck, &a, p->cgrid_clusters, st))) return TFFT_ERR_CUDA;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TFFT_OK;
+}
+
+template <typename T>
 int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
     typedef typename Cplx<T>::type C;
+    if (p->ck) return launch_cluster<T>(p, in, out, st);
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
     if (p->if_ft && !p->ft_accumulate) {
         if (!cuda_ok(p, cudaMemsetAsync(p->ft_count, 0, 6 * sizeof(unsigned int), st))) return TFFT_ERR_CUDA;
@@ -351,6 +391,17 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
 
     DeviceGuard guard(device);
     if (!guard.ok) return TFFT_ERR_CUDA;
+
+    // Sizes the built-in single-pass table names run as ONE cluster kernel (no FT variant of it
+    // exists, and a caller's own parameter file always means the launches that file describes).
+    if (!if_ft && !(param_csv && param_csv[0])) {
+        const int logg = builtin_single_pass_cluster(dtype, logN);
+        if (logg >= 0) {
+            const int rc = tfft_plan_create_single_pass(plan, logN, batch, dtype, logg, thread_bs, device);
+            if (rc == TFFT_OK) return rc;
+            *plan = nullptr;  // e.g. no room for a cluster on this device: fall back to the launches of the row
+        }
+    }
 
     tfft_plan p = new (std::nothrow) tfft_plan_s();
     if (!p) return TFFT_ERR_ALLOC;
@@ -437,6 +488,42 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
     *plan = p;
     return TFFT_OK;
 }
+
+int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int dtype, int log_cluster, int thread_bs,
+                                 int device) {
+    if (!plan) return TFFT_ERR_BAD_ARG;
+    *plan = nullptr;
+    if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 1 || device < 0)
+        return TFFT_ERR_BAD_ARG;
+    const ClusterKernel* ck = find_cluster_kernel(dtype, logN, log_cluster);
+    if (!ck) return TFFT_ERR_UNSUPPORTED;
+    DeviceGuard guard(device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (cluster_kernel_fits(*ck) < 1) return TFFT_ERR_UNSUPPORTED;
+    const long long clusters = (batch + thread_bs - 1) / thread_bs;
+    if ((clusters << ck->logg) > 2147483647LL) return TFFT_ERR_TOO_LARGE;
+    tfft_plan p = new (std::nothrow) tfft_plan_s();
+    if (!p) return TFFT_ERR_ALLOC;
+    p->logn = logN;
+    p->batch = batch;
+    p->dtype = dtype;
+    p->thread_bs = thread_bs;
+    p->device = device;
+    p->n_launch = 1;
+    p->ck = ck;
+    p->cgrid_clusters = (unsigned)clusters;
+    const bool ok = dtype == TFFT_FLOAT2 ? build_cluster_tables<float>(p) : build_cluster_tables<double>(p);
+    if (!ok) {
+        const int status = p->last_cuda_error ? TFFT_ERR_CUDA : TFFT_ERR_ALLOC;
+        for (void* q : p->allocs) cudaFree(q);
+        delete p;
+        return status;
+    }
+    *plan = p;
+    return TFFT_OK;
+}
+
+int tfft_plan_cluster_size(tfft_plan p) { return p ? (p->ck ? (1 << p->ck->logg) : 0) : TFFT_ERR_BAD_ARG; }
 
 int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
     if (!p || !in || !out) return TFFT_ERR_BAD_ARG;
@@ -572,7 +659,14 @@ int tfft_plan_info(tfft_plan p, int* info) {
     info[0] = p->n_launch;
     for (int i = 0; i < 3; ++i) {
         int* o = info + 1 + 6 * i;
-        if (i < p->n_launch) {
+        if (i == 0 && p->ck) {
+            o[0] = p->logn;
+            o[1] = 1;
+            o[2] = 2 << p->ck->lr;
+            o[3] = (int)(p->cgrid_clusters << p->ck->logg);
+            o[4] = p->ck->threads;
+            o[5] = (int)p->ck->smem;
+        } else if (i < p->n_launch) {
             const LaunchDesc& d = p->L[i];
             o[0] = d.logm;
             o[1] = 1 << d.logc;

@@ -34,6 +34,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#ifndef TFFT_F32X2
+#define TFFT_F32X2 1  // complex64 butterflies add and subtract with the packed f32x2 instructions of sm_100
+#endif
 #ifndef TFFT_FT_OCC
 #define TFFT_FT_OCC 3  // quarters of the plain kernels' resident-thread target that the FT variants aim for
 #endif
@@ -84,12 +87,38 @@ struct KernelArgs {
 // ---------------------------------------------------------------- complex helpers
 template <typename C> __device__ __forceinline__ C cadd(C a, C b) { C r; r.x = a.x + b.x; r.y = a.y + b.y; return r; }
 template <typename C> __device__ __forceinline__ C csub(C a, C b) { C r; r.x = a.x - b.x; r.y = a.y - b.y; return r; }
+#if TFFT_F32X2
+// sm_100 packed single precision: one instruction adds (subtracts) both components of a
+// complex value held in an aligned register pair.  a - b is formed as fma(b, -1, a), which
+// rounds exactly like the subtraction, so results are bit-identical to the scalar form.
+template <> __device__ __forceinline__ float2 cadd<float2>(float2 a, float2 b) { return __fadd2_rn(a, b); }
+template <> __device__ __forceinline__ float2 csub<float2>(float2 a, float2 b) {
+    return __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);
+}
+#endif
 template <typename C> __device__ __forceinline__ C cmul(C a, C b) {
     C r;
     r.x = a.x * b.x - a.y * b.y;
     r.y = a.x * b.y + a.y * b.x;
     return r;
 }
+
+// Per-thread checksum accumulator: acc += v.x * w.x + v.y * w.y.  complex64 keeps the two
+// products in the halves of one packed register pair (one f32x2 fma per element instead of two
+// scalar ones) and adds the halves when the tile is done; complex128 accumulates in a scalar.
+template <typename T> struct FtAcc { typedef T type; };
+template <typename T> __device__ __forceinline__ void acc_fma(T& acc, typename Cplx<T>::type v, typename Cplx<T>::type w) {
+    acc = fma(v.x, w.x, acc);
+    acc = fma(v.y, w.y, acc);
+}
+template <typename T> __device__ __forceinline__ T acc_sum(T acc) { return acc; }
+template <typename A> __device__ __forceinline__ A acc_zero() { return A(0); }
+#if TFFT_F32X2
+template <> struct FtAcc<float> { typedef float2 type; };
+__device__ __forceinline__ void acc_fma(float2& acc, float2 v, float2 w) { acc = __ffma2_rn(v, w, acc); }
+__device__ __forceinline__ float acc_sum(float2 acc) { return acc.x + acc.y; }
+template <> __device__ __forceinline__ float2 acc_zero<float2>() { return make_float2(0.0f, 0.0f); }
+#endif
 
 // cos(2*pi*k/32), k = 0..8
 template <typename T> __device__ __forceinline__ constexpr T cos32_tab(int k) {
@@ -255,8 +284,9 @@ struct Fft {
     // weights are NOT kept here: 2E registers per thread cost more (spills or occupancy)
     // than re-reading them per tile from the L1-resident table.
     struct FtRegs {
-        T al[3], be[3];  // fold weights of the right checksum, rotated by s mod 3
+        C ab[3];  // fold weights (alpha, beta) of the right checksum, rotated by s mod 3
     };
+    typedef typename FtAcc<T>::type A;  // checksum accumulator of one tile
 
     template <int ST> static __device__ __forceinline__ constexpr int logR() { return K::stage_logr(ST); }
     template <int ST> static __device__ __forceinline__ constexpr int logP() { return K::stage_logp(ST); }
@@ -335,7 +365,7 @@ struct Fft {
     // F(sum of inputs); the located tile's stored outputs get sum(y) - F(sum(x)) subtracted)
     template <int LR, bool DO_FT, int CS>
     static __device__ __forceinline__ void finish(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g, int s, int c,
-                                                  const FtRegs& f, T& tout) {
+                                                  const FtRegs& f, A& tout) {
         constexpr int R = 1 << LR, NB = E / R;
         C y[E];
 #pragma unroll
@@ -345,11 +375,7 @@ struct Fft {
         if (DO_FT) {
             constexpr int t3 = (K::LOGTPL & 1) ? 2 : 1;  // TPL mod 3
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                const int cls = (i * t3) % 3;
-                tout = fma(y[i].x, f.al[cls], tout);
-                tout = fma(y[i].y, f.be[cls], tout);
-            }
+            for (int i = 0; i < E; ++i) acc_fma(tout, y[i], f.ab[(i * t3) % 3]);
         }
         if constexpr (CS != 0) {
             C* sy = sm + K::SMEM_ELEMS + E * K::THREADS + threadIdx.x;
@@ -422,7 +448,7 @@ struct Fft {
 
     template <int ST, bool DO_FT, int CS>
     static __device__ __forceinline__ void stage(C (&v)[E], C* sm, const KernelArgs<T>& a, const Geom& g,
-                                                 const FtRegs& f, T& tout) {
+                                                 const FtRegs& f, A& tout) {
         constexpr int LR = logR<ST>(), R = 1 << LR, LP = logP<ST>(), P = 1 << LP, NB = E / R;
         constexpr bool LASTST = (ST == K::S - 1);
         constexpr bool CF = LASTST ? K::CFAST_OUT : K::CFAST_IN;
@@ -474,7 +500,7 @@ struct Fft {
     // tile's left and right checksums.
     template <bool DO_FT, bool DO_INJ, int CS = 0>
     static __device__ __forceinline__ void tile(const KernelArgs<T>& a, C* sm, long long tile_id, bool inject,
-                                                const FtRegs& f, T& tin, T& tout) {
+                                                const FtRegs& f, A& tin, A& tout) {
         static_assert(CS == 0 || (!K::STAGED_IO && ROLE != ROLE_FIRST), "checksum correction: single and last launches only");
         const Geom g = decode(a, tile_id);
         int s, c;
@@ -522,11 +548,7 @@ struct Fft {
             // fold(x * c) = x.x * (c.x + c.y) + x.y * (c.x - c.y); rows s + i*TPL, coalesced over s
             const C* wt = a.cks + s;
 #pragma unroll
-            for (int i = 0; i < E; ++i) {
-                const C w = __ldg(wt + i * TPL);
-                tin = fma(v[i].x, w.x, tin);
-                tin = fma(v[i].y, w.y, tin);
-            }
+            for (int i = 0; i < E; ++i) acc_fma(tin, v[i], __ldg(wt + i * TPL));
         }
         if (DO_INJ) {
             if (inject && threadIdx.x == 0) v[0].x += a.err_inj;
@@ -544,7 +566,7 @@ struct Fft {
         const long long grid = gridDim.x;
         if (FT == FT_OFF) {
             FtRegs f;
-            T tin = 0, tout = 0;
+            A tin = acc_zero<A>(), tout = acc_zero<A>();
             for (int it = 0; it < a.tiles_per_cta; ++it) {
                 const long long t = blockIdx.x + it * grid;
                 if (t >= a.n_tiles) break;
@@ -566,8 +588,8 @@ struct Fft {
 #pragma unroll
             for (int t = 0; t < 3; ++t) {
                 const int j = (s3 + t) % 3;
-                f.al[t] = j == 0 ? alpha[0] : (j == 1 ? alpha[1] : alpha[2]);
-                f.be[t] = j == 0 ? beta[0] : (j == 1 ? beta[1] : beta[2]);
+                f.ab[t].x = j == 0 ? alpha[0] : (j == 1 ? alpha[1] : alpha[2]);
+                f.ab[t].y = j == 0 ? beta[0] : (j == 1 ? beta[1] : beta[2]);
             }
         }
         const bool hit = a.inj_on && ((int)(blockIdx.x % (unsigned)a.inj_period) == a.inj_phase);
@@ -584,8 +606,9 @@ struct Fft {
         for (int it = 0; it < a.tiles_per_cta; ++it) {
             const long long t = blockIdx.x + it * grid;
             if (t >= a.n_tiles) break;
-            T tin = 0, tout = 0;
-            tile<true, true, CSACC>(a, sm, t, hit && it == inj_it, f, tin, tout);
+            A tin2 = acc_zero<A>(), tout2 = acc_zero<A>();
+            tile<true, true, CSACC>(a, sm, t, hit && it == inj_it, f, tin2, tout2);
+            const T tin = acc_sum(tin2), tout = acc_sum(tout2);
             acc_in += tin;
             acc_out += tout;
             acc_w = fma(T(it + 1), tin - tout, acc_w);
@@ -630,7 +653,7 @@ struct Fft {
             // recompute the located tile from the untouched input (fft_codegen.py:149-193)
             const int k = s_k;
             if (k >= 1 && k <= done) {
-                T tin = 0, tout = 0;
+                A tin = acc_zero<A>(), tout = acc_zero<A>();
                 tile<false, false>(a, sm, blockIdx.x + (long long)(k - 1) * grid, false, f, tin, tout);
                 if (threadIdx.x == 0) atomicAdd(a.ft_count + 1, 1u);
             }
@@ -639,7 +662,7 @@ struct Fft {
             // transform the summed inputs and take sum(y) - F(sum(x)) off the located tile's outputs
             const int k = s_k;
             if (k >= 1 && k <= done) {
-                T tin = 0, tout = 0;
+                A tin = acc_zero<A>(), tout = acc_zero<A>();
                 tile<false, false, 2>(a, sm, blockIdx.x + (long long)(k - 1) * grid, false, f, tin, tout);
                 if (threadIdx.x == 0) atomicAdd(a.ft_count + 1, 1u);
             }

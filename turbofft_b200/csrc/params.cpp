@@ -1,5 +1,6 @@
 #include "params.h"
 
+#include <cstdio>
 #include <cstdlib>
 #include <fstream>
 #include <sstream>
@@ -94,5 +95,23 @@ static const char* k_builtin_double2 =
     ;
 
 const char* builtin_param_csv(int dtype) { return dtype == 0 ? k_builtin_float2 : k_builtin_double2; }
+
+static const char* k_single_pass_float2 =
+#include "generated/default_single_pass_float2.inc"
+    ;
+static const char* k_single_pass_double2 =
+#include "generated/default_single_pass_double2.inc"
+    ;
+
+int builtin_single_pass_cluster(int dtype, int logn) {
+    std::istringstream ss(dtype == 0 ? k_single_pass_float2 : k_single_pass_double2);
+    std::string line;
+    while (std::getline(ss, line)) {
+        if (line.find_first_not_of(" \t\r\n") == std::string::npos || line[line.find_first_not_of(" \t")] == '#') continue;
+        int l = -1, g = -1;
+        if (sscanf(line.c_str(), "%d , %d", &l, &g) == 2 && l == logn) return g;
+    }
+    return -1;
+}
 
 }  // namespace tfft

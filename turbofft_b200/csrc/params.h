@@ -27,5 +27,9 @@ const char* builtin_param_csv(int dtype);
 // Structural checks shared by the planner and the tests: 1..3 launches, sizes add
 // up to logN, BS and n powers of two, n <= 32.
 bool validate_row(const ParamRow& r, std::string& err);
+// Built-in single-pass table (param/B200/single_pass_<dtype>.csv, lines "logN, log2 cluster
+// size"): log2 of the cluster size the size logN runs with as one cluster kernel, or -1 if
+// the size is not in the table and runs the launches of its parameter row.
+int builtin_single_pass_cluster(int dtype, int logn);
 
 }  // namespace tfft
