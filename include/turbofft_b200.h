@@ -154,6 +154,16 @@ int tfft_ft_diag(tfft_plan plan, int launch, double* diag, int cap_blocks);
 
 int tfft_plan_destroy(tfft_plan plan);
 
+/* Checked build only (the library compiled with -DTFFT_BOUNDS_CHECK=1,
+ * libturbofft_b200_check.so): every global load and store of the data buffers compares its
+ * element index with the plan's batch * N; an access outside is skipped and the first one
+ * is recorded.  Returns 0 if the most recent execs stayed inside, 1 if not (*bad_index = the
+ * element index, *site = 1/2 load, 3/4 store; the record is cleared), TFFT_ERR_UNSUPPORTED
+ * in the normal build.  The reference has no such check, and its stale generated kernels
+ * for float2 logN 2..4 index out of bounds
+ * (include/code_gen/generated/float2/fft_radix_2_logN_4_upload_0.cuh:67-77). */
+int tfft_bounds_status(tfft_plan plan, long long* bad_index, int* site);
+
 /* No counterpart in the reference.  One-shot transform for callers that cannot allocate
  * device memory when they call (no cudaMalloc allowed: pool-managed regions, allocation-free
  * service loops, devices whose memory is fully handed out).  Runs the built-in multi-launch

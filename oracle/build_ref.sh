@@ -3,10 +3,11 @@
 # kernels, read in place from $REF) behind oracle/ref_harness.cu for sm_100a.
 # Outputs go only to oracle/_ref/ (git-ignored): libturbofft_ref.so and a copy of
 # the reference's A100 parameter tables, which its launch protocol reads at run time.
-# Needs the reference tree; on a machine without it the prebuilt files are used as is.
+# Needs the reference tree ($TURBOFFT_REFERENCE, else a checkout named "reference" beside this
+# repository); on a machine without it the prebuilt files are used as is.
 set -euo pipefail
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${TURBOFFT_REFERENCE:-/root/reference}"
+REF="${TURBOFFT_REFERENCE:-$HERE/../../reference}"
 OUT="$HERE/_ref"
 if [ ! -f "$REF/main.cu" ]; then
     echo "[build_ref] reference tree not found at $REF; keeping prebuilt $OUT" >&2

@@ -142,3 +142,16 @@ def test_oracle_matches_reference_kernel_outputs(path):
         # the reference's per-component test, with head-room for fp32 rounding of both sides
         ok, i, comp = orc.compare_data(g[key], ref.astype(dtype), 1e-3)
         assert ok, (key, i, comp)
+
+
+def test_dft_bins_by_row_blocks_matches_fft():
+    """The regrouped direct sum used to spot-check very long transforms equals the FFT bins,
+    whichever way the rows are split over callers."""
+    rng = np.random.default_rng(5)
+    n1, n2 = 64, 128
+    x = (rng.uniform(-1, 1, n1 * n2) + 1j * rng.uniform(-1, 1, n1 * n2)).astype(np.complex64)
+    bins = np.array([0, 1, 77, n1 * n2 // 2, n1 * n2 - 1, 4097])
+    inner = sum(orc.dft_bins_partial(x[r * n2:(r + 16) * n2], r, n1, n2, bins) for r in range(0, n1, 16))
+    got = orc.dft_bins_finish(inner, n1, n2, bins)
+    assert np.allclose(got, orc.fft_forward(x)[bins], rtol=1e-11, atol=1e-9)
+    assert np.allclose(got, orc.dft_bins(x, bins), rtol=1e-11, atol=1e-9)

@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libturbofft_b200.so")
+# TURBOFFT_B200_LIB selects another build of the same library (the bounds-checked one,
+# libturbofft_b200_check.so, for debugging); there is still no fallback if it is missing.
+LIB_PATH = os.environ.get("TURBOFFT_B200_LIB") or os.path.join(PKG, "libturbofft_b200.so")
 
 TFFT_OK = 0
 STATUS = {
@@ -37,6 +39,7 @@ SIGNATURES = {
     "tfft_set_ft_accumulate": (C.c_int, [C.c_void_p, C.c_int]),
     "tfft_ft_diag": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_double), C.c_int]),
     "tfft_plan_destroy": (C.c_int, [C.c_void_p]),
+    "tfft_bounds_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_longlong), C.POINTER(C.c_int)]),
     "tfft_exec_static": (C.c_int, [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "tfft_last_cuda_error": (C.c_int, [C.c_void_p]),
     "tfft_status_string": (C.c_char_p, [C.c_int]),

@@ -61,6 +61,10 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hdrs)
 
 
+CHECK_LIB = os.path.join(PKG, "libturbofft_b200_check.so")
+CHECK_FLAGS = ("-DTFFT_BOUNDS_CHECK=1",)
+
+
 def _compile(src: str, obj: str, extra=()) -> str:
     cmd = [nvcc()] + NVCC_FLAGS + list(extra) + ["-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -69,20 +73,20 @@ def _compile(src: str, obj: str, extra=()) -> str:
     return obj
 
 
-def _objects(sources, jobs: int, verbose: bool):
+def _objects(sources, jobs: int, verbose: bool, extra=(), suffix: str = ""):
     os.makedirs(OBJ, exist_ok=True)
     hdr_time = _newest_header()
     todo, objs = [], []
     for src in sources:
         rel = os.path.relpath(src, CSRC).replace(os.sep, "_")
-        obj = os.path.join(OBJ, os.path.splitext(rel)[0] + ".o")
+        obj = os.path.join(OBJ, os.path.splitext(rel)[0] + suffix + ".o")
         objs.append(obj)
         if not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time):
             todo.append((src, obj))
     if verbose and todo:
         print(f"[build] compiling {len(todo)} of {len(sources)} translation units with {jobs} jobs")
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
-        for f in [ex.submit(_compile, s, o) for s, o in todo]:
+        for f in [ex.submit(_compile, s, o, extra) for s, o in todo]:
             f.result()
     return objs, bool(todo)
 
@@ -100,6 +104,15 @@ def build_all(verbose: bool = True, jobs: int | None = None, with_cli: bool = Tr
             raise RuntimeError(f"link failed:\n{res.stderr}")
         if verbose:
             print(f"[build] linked {LIB}")
+    # the same library with every global index of the data buffers checked (tfft_bounds_status)
+    kobjs, kchanged = _objects(core + gen, jobs, verbose, CHECK_FLAGS, "_check")
+    if kchanged or not os.path.exists(CHECK_LIB):
+        cmd = [nvcc(), "-shared", "-o", CHECK_LIB] + kobjs + ["-gencode", "arch=compute_100a,code=sm_100a"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stderr}")
+        if verbose:
+            print(f"[build] linked {CHECK_LIB}")
     cmp_src = os.path.join(CSRC, "cufft_compare.cu")
     if os.path.exists(cmp_src):
         cobjs, cchanged = _objects([cmp_src], jobs, verbose)

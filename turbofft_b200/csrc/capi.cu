@@ -91,6 +91,7 @@ struct tfft_plan_s {
     void* scratch2 = nullptr;          // 3-launch plans that correct: the middle launch writes here, so that
                                        // its own input survives for the recompute of a located tile
     unsigned int* ft_count = nullptr;  // [3][2]
+    unsigned long long* oob = nullptr;  // checked build: first out-of-range access of the last exec
     size_t owned_bytes = 0;
     double err_inj = TFFT_DEFAULT_ERR_INJ;
     double err_smoothing = TFFT_DEFAULT_ERR_SMOOTHING;
@@ -352,6 +353,8 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         a.err_inj = (T)p->err_inj;
         a.err_smoothing = (T)p->err_smoothing;
         a.err_threshold = (T)p->err_threshold;
+        a.n_elems = p->batch << p->logn;
+        a.oob = p->oob;
         a.ft_located = d.ft_located;
         a.ft_count = p->ft_count ? p->ft_count + 2 * i : nullptr;
         a.ft_diag = p->diag ? (T*)d.ft_diag : nullptr;
@@ -471,6 +474,12 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
             if (!p->scratch2) status = TFFT_ERR_ALLOC;
         }
     }
+#if TFFT_BOUNDS_CHECK
+    if (status == TFFT_OK) {
+        p->oob = (unsigned long long*)dev_alloc(p, sizeof(unsigned long long));
+        if (!p->oob || !cuda_ok(p, cudaMemset(p->oob, 0, sizeof(unsigned long long)))) status = TFFT_ERR_ALLOC;
+    }
+#endif
     if (status == TFFT_OK && p->if_ft) {
         p->ft_count = (unsigned int*)dev_alloc(p, 6 * sizeof(unsigned int));
         if (!p->ft_count) status = TFFT_ERR_ALLOC;
@@ -759,6 +768,31 @@ int tfft_set_ft_accumulate(tfft_plan p, int enable) {
     if (!p) return TFFT_ERR_BAD_ARG;
     p->ft_accumulate = enable ? 1 : 0;
     return TFFT_OK;
+}
+
+int tfft_bounds_status(tfft_plan p, long long* bad_index, int* site) {
+    if (!p) return TFFT_ERR_BAD_ARG;
+    if (bad_index) *bad_index = -1;
+    if (site) *site = 0;
+#if TFFT_BOUNDS_CHECK
+    if (!p->oob) return TFFT_ERR_UNSUPPORTED;  // single-pass plans carry no checks
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaStreamSynchronize(p->last_stream))) return TFFT_ERR_CUDA;
+    unsigned long long w = 0;
+    if (!cuda_ok(p, cudaMemcpy(&w, p->oob, sizeof(w), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
+    if (w >> 63) {
+        long long idx = (long long)(w & ((1ULL << 56) - 1));
+        if (idx & (1LL << 55)) idx |= ~((1LL << 56) - 1);  // sign of a negative index
+        if (bad_index) *bad_index = idx;
+        if (site) *site = (int)((w >> 56) & 0x7f);
+        if (!cuda_ok(p, cudaMemset(p->oob, 0, sizeof(w)))) return TFFT_ERR_CUDA;
+        return 1;
+    }
+    return TFFT_OK;
+#else
+    return TFFT_ERR_UNSUPPORTED;
+#endif
 }
 
 int tfft_enable_ft_diag(tfft_plan p, int enable) {

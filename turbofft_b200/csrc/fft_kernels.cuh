@@ -37,6 +37,9 @@
 #ifndef TFFT_F32X2
 #define TFFT_F32X2 1  // complex64 butterflies add and subtract with the packed f32x2 instructions of sm_100
 #endif
+#ifndef TFFT_BOUNDS_CHECK
+#define TFFT_BOUNDS_CHECK 0  // 1: every global load/store index of the data buffers is checked (see KernelArgs::oob)
+#endif
 #ifndef TFFT_FT_OCC
 #define TFFT_FT_OCC 3  // quarters of the plain kernels' resident-thread target that the FT variants aim for
 #endif
@@ -79,6 +82,11 @@ struct KernelArgs {
     T err_inj;
     T err_smoothing;
     T err_threshold;
+    // Checked build (TFFT_BOUNDS_CHECK): extent of `in` / `out` in elements and a status word that
+    // receives the first out-of-range access (bit 63 set, bits 56..62 the access site, bits 0..55
+    // the element index); the offending access is skipped.  Unused in the normal build.
+    long long n_elems;
+    unsigned long long* oob;
     int* ft_located;          // per block: located tile iteration (1-based) or -1
     unsigned int* ft_count;   // [0] blocks that detected, [1] tiles recomputed
     T* ft_diag;               // per block: delta, S, delta_w (may be null)
@@ -288,6 +296,19 @@ struct Fft {
     };
     typedef typename FtAcc<T>::type A;  // checksum accumulator of one tile
 
+    // Checked build only: is element index idx inside the data buffers?  Records the first offender.
+    static __device__ __forceinline__ bool in_range(const KernelArgs<T>& a, long long idx, int site) {
+#if TFFT_BOUNDS_CHECK
+        if (idx < 0 || idx >= a.n_elems) {
+            if (a.oob)
+                atomicCAS(a.oob, 0ULL,
+                          (1ULL << 63) | ((unsigned long long)site << 56) | ((unsigned long long)idx & ((1ULL << 56) - 1)));
+            return false;
+        }
+#endif
+        return true;
+    }
+
     template <int ST> static __device__ __forceinline__ constexpr int logR() { return K::stage_logr(ST); }
     template <int ST> static __device__ __forceinline__ constexpr int logP() { return K::stage_logp(ST); }
     // first entry of stage ST in the stage-twiddle table: sum over earlier stages of log2(R) * M / R
@@ -434,12 +455,14 @@ struct Fft {
 #pragma unroll
             for (int k = 0; k < K::M; ++k) {
                 const int fl = k * K::C + (int)threadIdx.x;
-                if (fl < valid) dst[fl] = sm[(fl >> LOGM) * (K::M + 1) + (fl & (K::M - 1))];
+                if (fl < valid && in_range(a, g.out_base + fl, 3)) dst[fl] = sm[(fl >> LOGM) * (K::M + 1) + (fl & (K::M - 1))];
             }
         } else if (c < g.ncols) {
-            C* dst = a.out + g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
+            const long long o0 = g.out_base + (long long)c * g.out_cs + (long long)s * g.out_rs;
+            C* dst = a.out + o0;
 #pragma unroll
             for (int i = 0; i < E; ++i) {
+                if (!in_range(a, o0 + (long long)i * TPL * g.out_rs, 4)) continue;
                 if (CS == 2) dst[(long long)i * TPL * g.out_rs] = csub(dst[(long long)i * TPL * g.out_rs], y[i]);
                 else dst[(long long)i * TPL * g.out_rs] = y[i];
             }
@@ -521,16 +544,20 @@ struct Fft {
                 const int fl = k * K::C + (int)threadIdx.x;
                 C t;
                 t.x = t.y = T(0);
-                if (fl < valid) t = src[fl];
+                if (fl < valid && in_range(a, g.in_base + fl, 1)) t = src[fl];
                 sm[(fl >> LOGM) * (K::M + 1) + (fl & (K::M - 1))] = t;
             }
             __syncthreads();
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i] = sm[c * (K::M + 1) + i];
         } else if (c < g.ncols) {
-            const C* src = a.in + g.in_base + (long long)c * g.in_cs + (long long)s * g.in_rs;
+            const long long i0 = g.in_base + (long long)c * g.in_cs + (long long)s * g.in_rs;
+            const C* src = a.in + i0;
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = src[(long long)i * TPL * g.in_rs];
+            for (int i = 0; i < E; ++i) {
+                if (in_range(a, i0 + (long long)i * TPL * g.in_rs, 2)) v[i] = src[(long long)i * TPL * g.in_rs];
+                else v[i].x = v[i].y = T(0);
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
