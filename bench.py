@@ -310,9 +310,10 @@ def also_single_gpu(a, torch, tf, dev, x, y, stream, points, ours_ms, ours_per, 
     cu["per_point_ours_over_cufft_speed"] = {str(l): (round(cu["per_point_ms"][str(l)] / o, 3) if cu["per_point_ms"][str(l)] else None)
                                              for l, o in zip(points, ours_per)}
     also["cufft"] = cu
-    ft = {"thread_bs": 8, "baseline": "the headline sweep (FT off, thread_bs %d)" % a.thread_bs}
+    ft = {"thread_bs": "per size, the tuned table (plans created with thread_bs = 0)",
+          "baseline": "the headline sweep (FT off, thread_bs %d)" % a.thread_bs}
     for name, if_err in (("detect", 0), ("inject_correct", 1)):
-        plans = {l: tf.Plan(l, 1 << (lt - l), a.datatype, if_ft=1, if_err=if_err, thread_bs=8, device=dev.index) for l in points}
+        plans = {l: tf.Plan(l, 1 << (lt - l), a.datatype, if_ft=1, if_err=if_err, thread_bs=0, device=dev.index) for l in points}
         ms, per = time_sweep(torch, plans, points, x, y, stream, steps)
         nd, nc, loc = plans[points[-1]].ft_status()
         ft[name] = {"ms_per_step": ms, "overhead_pct": 100 * (ms / ours_ms - 1),

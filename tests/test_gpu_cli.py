@@ -28,8 +28,9 @@ def test_readme_verify_case(torch_cuda, datatype):
 
 
 def test_benchmark_line_format(torch_cuda):
-    """--if_bench 1 prints 'turboFFT, logN, logBS, ms, GFLOPS, GB/s' per batch size (main.cu:70)."""
-    r = _run("--if_bench", "1", "--logN", "12", "--bs", "64", "--bs_end", "128", "--bs_gap", "2")
+    """--if_profile 1 prints 'turboFFT, logN, logBS, ms, GFLOPS, GB/s' per batch size from --bs to
+    --bs_end in steps of --bs_gap, after the cuFFT lines (main.cu:70,104-111)."""
+    r = _run("--if_bench", "0", "--if_profile", "1", "--logN", "12", "--bs", "64", "--bs_end", "128", "--bs_gap", "64")
     assert r.returncode == 0, r.stderr
     rows = [ln for ln in r.stdout.splitlines() if ln.startswith("turboFFT,")]
     assert len(rows) == 2
@@ -39,7 +40,8 @@ def test_benchmark_line_format(torch_cuda):
 
 
 def test_ft_mode_reports_counts(torch_cuda):
-    r = _run("--if_bench", "1", "--logN", "10", "--bs", "256", "--bs_end", "256", "--if_ft", "1", "--if_err", "1", "--thread_bs", "4")
+    r = _run("--if_bench", "0", "--if_profile", "1", "--logN", "10", "--bs", "256", "--bs_end", "256", "--if_ft", "1",
+             "--if_err", "1", "--thread_bs", "4")
     assert r.returncode == 0, r.stderr
     m = re.search(r"turboFFT_ft, 10, 8, blocks=(\d+), detected=(\d+), corrected=(\d+)", r.stdout)
     assert m and m.group(1) == m.group(2) == m.group(3)

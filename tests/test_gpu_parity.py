@@ -195,3 +195,33 @@ def test_errors(torch_cuda):
         tf.Plan(10, 0, 0)
     with pytest.raises(tf.TurboFFTError):
         tf.Plan(10, 4, 0, param_csv="/nonexistent/param.csv")
+
+
+def test_tuner_run_times_the_current_row(torch_cuda, tmp_path):
+    """`python -m turbofft_b200.tune run` on one size: the shipped row is timed (candidates whose
+    kernels are not compiled are skipped), thread_bs is searched for FT off and on, and the result
+    file has what `tune apply` reads."""
+    import json
+
+    from turbofft_b200 import tune
+
+    out = tmp_path / "r.json"
+    tune.main(["run", "--datatype", "float2", "--lo", "10", "--hi", "10", "--reps", "1", "--burn", "1", "--log-total", "20",
+               "--thread-bs", "1,4", "--out", str(out)])
+    res = json.loads(out.read_text())["10"]
+    assert res["tried"] >= 1 and res["best"][0] > 0 and res["current_ms"] > 0
+    assert set(res["thread_bs_ms"]) == {"0:1", "0:4", "1:1", "1:4"} and res["thread_bs"][0] in (1, 4)
+
+
+def test_thread_bs_zero_follows_the_tuned_table(torch_cuda):
+    import turbofft_b200 as tf
+    from turbofft_b200 import planner
+
+    table = planner.load_thread_bs("float2")
+    logn, batch = 12, 64
+    x = orc.make_input(batch, 1 << logn, np.complex64, seed=1)
+    plan = tf.Plan(logn, batch, 0, thread_bs=0)
+    want = table.get(logn, (1, 1))[0]
+    assert plan.info()[0]["grid"] == -(-batch // want)          # one signal per tile at this size
+    y = plan(torch_cuda.from_numpy(x).cuda()).cpu().numpy()
+    assert orc.rel_l2(y, orc.fft_forward(x)) <= orc.tolerance(np.complex64, logn)

@@ -106,6 +106,96 @@ def test_four_step_distribution_logic_gloo(world, logn, natural):
     assert len(res) == world and all(e < 1e-12 for e in res.values()), res
 
 
+def _mismatch_worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        try:
+            mg.FourStepFFT(10 + (rank == 1), world, rank, HostBackend(torch))   # rank 1 plans another length
+            q.put((rank, "constructed"))
+        except ValueError as e:
+            q.put((rank, "refused: " + str(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mismatched_plans_are_refused_at_construction_gloo():
+    """A rank that describes another transform than its peers is caught before any data moves:
+    every rank raises at construction (nothing hangs, nothing is exchanged)."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    res = dict(q.get(timeout=10) for _ in range(2))
+    assert all(v.startswith("refused") for v in res.values()), res
+
+
+def _leaver_worker(rank, world, port, q):
+    import datetime
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    logn = 10
+    n = 1 << logn
+    x = orc.make_input(1, n, np.complex128, seed=1)[0]
+    b, e = mg.shard_range(n, world, rank)
+    fs = mg.FourStepFFT(logn, world, rank, HostBackend(torch))
+    xl = torch.from_numpy(x[b:e].copy())
+    fs(xl)                                   # step 1: everybody takes part
+    def leave(msg):
+        q.put((rank, msg))
+        q.close()
+        q.join_thread()                      # the message is on its way before the process goes
+        os._exit(0)                          # (the process group cannot be torn down cleanly any more)
+
+    if rank == world - 1:
+        leave("left")                        # leaves between steps, nothing of its own in flight
+    t0 = time.time()
+    try:
+        fs(xl)                               # step 2: one peer is gone
+        msg = "completed"
+    except Exception as ex:                  # noqa: BLE001 -- whatever the backend raises, it must raise
+        msg = f"error after {time.time() - t0:.1f} s: {type(ex).__name__}"
+    leave(msg)
+
+
+def test_rank_that_leaves_between_steps_ends_the_others_with_an_error_gloo():
+    """Failure detection without any device fault: a rank exits between two transforms; the
+    remaining ranks' next exchange ends with an error inside the process-group timeout instead of
+    hanging, so the caller can tear the job down."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    world = 4
+    procs = [ctx.Process(target=_leaver_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+        assert p.exitcode is not None, "a rank hung after its peer left"
+    res = dict(q.get(timeout=10) for _ in range(world))
+    assert res[world - 1] == "left"
+    assert all(res[r].startswith("error") for r in range(world - 1)), res
+
+
 def test_batch_sharding_is_communication_free_gloo():
     """Each rank transforms its own contiguous batch range; concatenation equals the whole."""
     x = orc.make_input(10, 64, np.complex128, seed=3)

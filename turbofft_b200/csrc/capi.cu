@@ -14,6 +14,13 @@
 #include <string>
 #include <vector>
 
+#ifndef TFFT_NVTX
+#define TFFT_NVTX 1  // NVTX ranges around plan creation and every exec (header-only NVTX v3; free without a tool attached)
+#endif
+#if TFFT_NVTX
+#include <nvtx3/nvToolsExt.h>
+#endif
+
 #include "../../include/turbofft_b200.h"
 #include "fft_kernels.cuh"
 #include "generated/ft_defaults.h"
@@ -74,6 +81,16 @@ struct DeviceGuard {
     }
 };
 
+// Named range on the calling host thread, visible to profilers that listen to NVTX.
+struct NvtxRange {
+#if TFFT_NVTX
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+#else
+    explicit NvtxRange(const char*) {}
+#endif
+};
+
 }  // namespace
 
 struct tfft_plan_s {
@@ -106,6 +123,7 @@ struct tfft_plan_s {
     int last_cuda_error = 0;
     std::vector<void*> allocs;
     std::string param_csv;            // empty = built-in table
+    char nvtx_name[64] = "tfft_exec";  // range name of this plan's execs
     // host-buffer pipeline (tfft_exec_host): sub-plans for one chunk / the ragged last chunk,
     // three internal streams and per-slot events
     tfft_plan chunk_plan = nullptr;
@@ -377,10 +395,12 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
                      const char* param_csv, int device) {
     if (!plan) return TFFT_ERR_BAD_ARG;
     *plan = nullptr;
-    if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 1 ||
+    if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 0 ||
         device < 0)
         return TFFT_ERR_BAD_ARG;
+    NvtxRange range("tfft_plan_create");
     if (if_err) if_ft = 1;  // as the reference CLI does (CommandLineParser.h:62-64)
+    if (thread_bs == 0) thread_bs = builtin_thread_bs(dtype, logN, if_ft);  // the tuned value of this size
     std::vector<ParamRow> rows;
     std::string err;
     if (param_csv && param_csv[0]) {
@@ -417,6 +437,8 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
     p->thread_bs = thread_bs;
     p->device = device;
     p->n_launch = row.launches;
+    snprintf(p->nvtx_name, sizeof(p->nvtx_name), "tfft_exec logN=%d batch=%lld %s ft=%d", logN, batch,
+             dtype == TFFT_FLOAT2 ? "c64" : "c128", p->if_ft + p->if_err);
     if (param_csv && param_csv[0]) p->param_csv = param_csv;
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
 
@@ -521,6 +543,8 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
     p->n_launch = 1;
     p->ck = ck;
     p->cgrid_clusters = (unsigned)clusters;
+    snprintf(p->nvtx_name, sizeof(p->nvtx_name), "tfft_exec logN=%d batch=%lld %s single-pass", logN, batch,
+             dtype == TFFT_FLOAT2 ? "c64" : "c128");
     const bool ok = dtype == TFFT_FLOAT2 ? build_cluster_tables<float>(p) : build_cluster_tables<double>(p);
     if (!ok) {
         const int status = p->last_cuda_error ? TFFT_ERR_CUDA : TFFT_ERR_ALLOC;
@@ -541,6 +565,7 @@ int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
     if (!guard.ok) return TFFT_ERR_CUDA;
     cudaStream_t st = (cudaStream_t)stream;
     p->last_stream = st;
+    NvtxRange range(p->nvtx_name);
     return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st) : launch_all<double>(p, in, out, st);
 }
 
@@ -632,6 +657,7 @@ static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host,
 
 int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* stream) {
     if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
+    NvtxRange range("tfft_exec_host");
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
     {

@@ -103,6 +103,26 @@ static const char* k_single_pass_double2 =
 #include "generated/default_single_pass_double2.inc"
     ;
 
+static const char* k_thread_bs_float2 =
+#include "generated/default_thread_bs_float2.inc"
+    ;
+static const char* k_thread_bs_double2 =
+#include "generated/default_thread_bs_double2.inc"
+    ;
+
+int builtin_thread_bs(int dtype, int logn, int ft) {
+    std::istringstream ss(dtype == 0 ? k_thread_bs_float2 : k_thread_bs_double2);
+    std::string line;
+    while (std::getline(ss, line)) {
+        int l = -1, off = 1, on = 1;
+        if (sscanf(line.c_str(), "%d , %d , %d", &l, &off, &on) == 3 && l == logn) {
+            const int v = ft ? on : off;
+            return v >= 1 ? v : 1;
+        }
+    }
+    return 1;
+}
+
 int builtin_single_pass_cluster(int dtype, int logn) {
     std::istringstream ss(dtype == 0 ? k_single_pass_float2 : k_single_pass_double2);
     std::string line;

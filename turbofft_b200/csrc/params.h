@@ -31,5 +31,8 @@ bool validate_row(const ParamRow& r, std::string& err);
 // size"): log2 of the cluster size the size logN runs with as one cluster kernel, or -1 if
 // the size is not in the table and runs the launches of its parameter row.
 int builtin_single_pass_cluster(int dtype, int logn);
+// Built-in thread_bs table (param/B200/thread_bs_<dtype>.csv, lines "logN, FT off, FT on"): what a
+// plan created with thread_bs = 0 uses; 1 for sizes that are not listed.
+int builtin_thread_bs(int dtype, int logn, int ft);
 
 }  // namespace tfft

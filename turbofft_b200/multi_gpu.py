@@ -123,6 +123,23 @@ class FourStepFFT:
         if self.n1 % world or self.n2 % world:
             raise ValueError("world size must divide both factors of the transform")
         self.be, self.group, self.natural = backend, group, natural_order
+        if world > 1:
+            self._agree()
+
+    def _agree(self):
+        """Every rank must describe the same transform: a rank built with another length or output
+        order would exchange blocks of the wrong shape (silently wrong data, or a collective that
+        never completes).  One all_gather of the description at construction; any difference raises
+        on every rank."""
+        import torch.distributed as dist
+
+        if not (dist.is_available() and dist.is_initialized()):
+            return
+        mine = (self.logn, self.world, bool(self.natural))
+        seen = [None] * self.world
+        dist.all_gather_object(seen, mine, group=self.group)
+        if any(s != mine for s in seen):
+            raise ValueError(f"ranks disagree on the transform (logn, world, natural_order): {seen}")
 
     def __call__(self, x_local):
         be, P, r = self.be, self.world, self.rank

@@ -71,6 +71,21 @@ def load_params(dtype: str, gpu: str = "B200", path: str | None = None) -> Dict[
         return parse_param_csv(f.read())
 
 
+def load_thread_bs(dtype: str, gpu: str = "B200") -> Dict[int, tuple]:
+    """param/<gpu>/thread_bs_<dtype>.csv: logN -> (thread_bs with FT off, with FT on); sizes that are
+    not listed use 1.  A plan created with thread_bs = 0 follows this table (the C++ planner reads the
+    copy compiled into the library)."""
+    path = os.path.join(PARAM_DIR, gpu, f"thread_bs_{dtype}.csv")
+    out: Dict[int, tuple] = {}
+    if os.path.exists(path):
+        for line in open(path):
+            s = line.strip()
+            if s and not s.startswith("#"):
+                tok = [int(t) for t in s.split(",")]
+                out[tok[0]] = (tok[1], tok[2])
+    return out
+
+
 def validate_row(r: ParamRow) -> None:
     if not 1 <= r.launches <= 3:
         raise ValueError("launches must be 1..3")

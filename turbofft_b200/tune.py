@@ -1,7 +1,11 @@
 """Tuner for param/<gpu>/param_<datatype>.csv (the reference's 11-column format, readme.md:46-67).
 
 The reference ships hand-tuned A100/T4 tables; this searches the same space on the machine
-it runs on: launch split (logN1..3), lines per block (BSi) and points per thread (ni).
+it runs on: launch split (logN1..3), lines per block (BSi), points per thread (ni) and -- per
+size, for the chosen row -- thread_bs, the tiles one block loops over (the reference leaves it to
+the command line, compile.sh:13-19, and records one table per value in data_ft/*.csv).  The
+thread_bs choices go to param/<gpu>/thread_bs_<datatype>.csv ("logN, FT off, FT on"), which a plan
+created with thread_bs = 0 follows.
 
   1. python -m turbofft_b200.tune emit --datatype float2          # CPU: candidate rows ->
         param/B200/extra_float2.csv, then `python -m turbofft_b200.build` compiles them
@@ -106,6 +110,19 @@ def cmd_emit(a):
     print(f"wrote {n} candidate rows to {path}")
 
 
+def _time_plan(torch, plan, x, y, stream, burn, reps):
+    for _ in range(burn):
+        plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
 def cmd_run(a):
     import torch
 
@@ -148,10 +165,27 @@ def cmd_run(a):
             if best is None or ms < best[0]:
                 best = (ms, row_text(r))
         rows.sort()
+        # thread_bs for the winning row, FT off and FT on (detect)
+        tbs_ms = {}
+        with tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False) as f:
+            f.write(best[1] + "\n")
+            path = f.name
+        for ft in (0, 1):
+            for tbs in a.thread_bs:
+                try:
+                    plan = tf.Plan(logn, 1 << (a.log_total - logn), dt, if_ft=ft, thread_bs=tbs, param_csv=path)
+                except tf.TurboFFTError:
+                    continue
+                tbs_ms[f"{ft}:{tbs}"] = _time_plan(torch, plan, x, y, stream, a.burn, a.reps)
+                plan.destroy()
+        os.unlink(path)
+        pick = {ft: min((v, int(k.split(":")[1])) for k, v in tbs_ms.items() if k.startswith(f"{ft}:"))[1]
+                for ft in (0, 1) if any(k.startswith(f"{ft}:") for k in tbs_ms)}
         results[str(logn)] = {"best": best, "current_ms": rows and next((m for m, t in rows if t == row_text(current[logn])), None),
-                              "top": rows[:5], "tried": len(rows)}
-        print(f"logN {logn}: best {best[0]:.3f} ms [{best[1]}] current {results[str(logn)]['current_ms']} ({len(rows)} tried)",
-              flush=True)
+                              "top": rows[:5], "tried": len(rows), "thread_bs_ms": tbs_ms,
+                              "thread_bs": [pick.get(0, 1), pick.get(1, 1)]}
+        print(f"logN {logn}: best {best[0]:.3f} ms [{best[1]}] current {results[str(logn)]['current_ms']} ({len(rows)} tried) "
+              f"thread_bs FT off/on {results[str(logn)]['thread_bs']}", flush=True)
     with open(a.out, "w") as f:
         json.dump(results, f, indent=1)
 
@@ -172,6 +206,17 @@ def cmd_apply(a):
     with open(path, "w") as f:
         f.write("\n".join(lines) + "\n")
     print(f"updated {path}")
+    # thread_bs table: keep what is there, replace the sizes that were measured
+    tpath = os.path.join(planner.PARAM_DIR, a.gpu, f"thread_bs_{a.datatype}.csv")
+    table = planner.load_thread_bs(a.datatype, a.gpu)
+    for key, r in res.items():
+        if "thread_bs" in r:
+            table[int(key)] = tuple(r["thread_bs"])
+    with open(tpath, "w") as f:
+        f.write("# thread_bs a plan created with thread_bs = 0 uses: logN, FT off, FT on (written by turbofft_b200.tune)\n")
+        for logn in sorted(table):
+            f.write(f"{logn}, {table[logn][0]}, {table[logn][1]}\n")
+    print(f"updated {tpath}")
 
 
 def main(argv=None):
@@ -188,6 +233,8 @@ def main(argv=None):
             p.add_argument("--reps", type=int, default=5)
             p.add_argument("--burn", type=int, default=2, help="untimed runs before the timed ones")
             p.add_argument("--out", default="tune_results.json")
+            p.add_argument("--thread-bs", type=lambda t: [int(v) for v in t.split(",")], default=[1, 2, 4, 8],
+                           help="thread_bs values tried for the winning row")
         if name == "apply":
             p.add_argument("--results", required=True)
             p.add_argument("--min-gain", type=float, default=0.01)
