@@ -199,6 +199,35 @@ long long tfft_launch_count(void);
  * of 16.  Stream ordered. */
 int tfft_stream_copy(const void* src, void* dst, size_t bytes, void* stream);
 
+/* One transform too long for one GPU, over several devices driven by ONE process (no counterpart
+ * in the reference, which is single-GPU; its device/default_fft.h:14 only notes the wish).
+ * N = 2^logN = N1 * N2 with N1 = 2^ceil(logN/2); rank r (= position in `devices`) holds
+ * elements [r * N / P, (r + 1) * N / P) of the signal in in[r] on devices[r].  Four-step:
+ * transposing exchange, N2/P local transforms of length N1, twiddled transposing exchange,
+ * N1/P local transforms of length N2.  The exchanges are kernels that store straight into the
+ * other devices' receive buffers over NVLink (peer access is enabled between all pairs; a
+ * device may appear more than once, which runs several ranks on one GPU); ranks are ordered
+ * by CUDA events only, nothing on a device waits for a peer.  pipeline = G >= 1 cuts every
+ * exchange into G pieces and overlaps piece g + 1 with the transforms of piece g (each rank's
+ * N1/P and N2/P must be multiples of 32 * G, else TFFT_ERR_UNSUPPORTED).
+ * Output: natural_order == 0: X[k1 + N1 * k2] at rank k1 / (N1 / P), out[rank][(k1 % (N1/P)) * N2 + k2]
+ * ("transposed out"); natural_order != 0: out[r] = X[r * N / P ...], one more exchange.
+ * if_ft: every local transform carries the fused two-sided checksums (detect only).
+ * The plan owns three buffers of N / P elements per device plus the local plans. */
+typedef struct tfft_mg_plan_s* tfft_mg_plan;
+int tfft_mg_plan_create(tfft_mg_plan* plan, int logN, int dtype, int if_ft, int n_devices, const int* devices,
+                        int natural_order, int pipeline);
+/* in, out: n_devices device pointers (in[r] may equal out[r]).  streams: n_devices cudaStream_t
+ * or NULL; if given, the work on devices[r] starts behind what streams[r] holds and streams[r]
+ * continues behind it.  Returns without synchronising; tfft_mg_sync waits for every device. */
+int tfft_mg_exec(tfft_mg_plan plan, const void* const* in, void* const* out, void* const* streams);
+int tfft_mg_sync(tfft_mg_plan plan);
+/* Blocks whose checksum test fired / tiles repaired, summed over all local transforms of all
+ * ranks since the last call of this function (synchronises). */
+int tfft_mg_ft_status(tfft_mg_plan plan, int* n_detected, int* n_corrected);
+int tfft_mg_last_cuda_error(tfft_mg_plan plan);
+int tfft_mg_destroy(tfft_mg_plan plan);
+
 /* Building blocks of the multi-GPU four-step transform (no counterpart in the
  * reference, which is single-GPU).  They work on local complex arrays in device
  * memory.

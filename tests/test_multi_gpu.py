@@ -401,3 +401,59 @@ def test_dma_exchange_geometry_numpy():
                     recv[j][doff + h * dpitch: doff + h * dpitch + width] = send[soff + h * spitch: soff + h * spitch + width]
     for j in range(P):
         assert np.array_equal(recv[j].reshape(cb, n1), x[:, j * cb:(j + 1) * cb].T)
+
+
+def _split_parts(torch, x, devices):
+    P = len(devices)
+    n = x.shape[0]
+    return [torch.from_numpy(x[r * n // P:(r + 1) * n // P].copy()).to(f"cuda:{d}") for r, d in enumerate(devices)]
+
+
+def _check_single_process(torch, dtype, logn, devices, natural, pipeline, if_ft=0):
+    npdt = np.complex64 if dtype == 0 else np.complex128
+    x = orc.make_input(1, 1 << logn, npdt, seed=logn + len(devices))[0]
+    fs = mg.SingleProcessFourStep(logn, dtype, devices, natural_order=natural, if_ft=if_ft, pipeline=pipeline)
+    try:
+        for _ in range(2):          # twice: the second call reuses the receive buffers behind the first
+            outs = fs(_split_parts(torch, x, devices))
+        y = np.concatenate([o.cpu().numpy() for o in outs])
+        ref = orc.fft_forward(x)
+        if not natural:
+            ref = ref.reshape(1 << fs.l2, 1 << fs.l1).T.reshape(-1)     # [k1][k2], rows block-distributed over ranks
+        assert orc.rel_l2(y, ref) <= orc.tolerance(npdt, logn)
+        if if_ft:
+            assert fs.ft_counts() == (0, 0)
+    finally:
+        fs.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,logn,ranks,natural,pipeline", [(0, 16, 1, False, 1), (1, 14, 1, True, 2), (0, 18, 2, False, 1),
+                                                              (0, 18, 2, True, 2), (1, 17, 4, False, 1), (0, 20, 4, True, 2),
+                                                              (1, 16, 2, False, 2)])
+def test_single_process_four_step_ranks_on_one_gpu(torch_cuda, dtype, logn, ranks, natural, pipeline):
+    """tfft_mg_* with every rank on device 0: the whole exchange / event logic of the multi-device
+    plan runs on one GPU (nothing in it waits on a peer, so ranks may share a device)."""
+    _check_single_process(torch_cuda, dtype, logn, [0] * ranks, natural, pipeline, if_ft=int(logn == 18))
+
+
+@pytest.mark.gpu
+def test_single_process_four_step_refuses_bad_plans(torch_cuda):
+    import ctypes as C
+
+    import turbofft_b200 as tf
+
+    lib = tf.lib()
+    h = C.c_void_p()
+    dev = (C.c_int * 4)(0, 0, 0, 0)
+    assert lib.tfft_mg_plan_create(C.byref(h), 20, 0, 0, 3, dev, 0, 1) == -1       # ranks not a power of two
+    assert lib.tfft_mg_plan_create(C.byref(h), 14, 0, 0, 4, dev, 0, 2) == -2       # shares too small for 2 pieces of 32 lines
+    assert lib.tfft_mg_plan_create(C.byref(h), 20, 7, 0, 2, dev, 0, 1) == -1       # no such datatype
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,logn,natural,pipeline", [(0, 22, False, 4), (1, 20, True, 2)])
+def test_single_process_four_step_two_gpus(torch_cuda, dtype, logn, natural, pipeline):
+    if torch_cuda.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _check_single_process(torch_cuda, dtype, logn, [0, 1], natural, pipeline, if_ft=1)

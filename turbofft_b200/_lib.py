@@ -41,6 +41,13 @@ SIGNATURES = {
     "tfft_plan_destroy": (C.c_int, [C.c_void_p]),
     "tfft_bounds_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_longlong), C.POINTER(C.c_int)]),
     "tfft_exec_static": (C.c_int, [C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "tfft_mg_plan_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int,
+                                      C.c_int]),
+    "tfft_mg_exec": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "tfft_mg_sync": (C.c_int, [C.c_void_p]),
+    "tfft_mg_ft_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tfft_mg_last_cuda_error": (C.c_int, [C.c_void_p]),
+    "tfft_mg_destroy": (C.c_int, [C.c_void_p]),
     "tfft_last_cuda_error": (C.c_int, [C.c_void_p]),
     "tfft_status_string": (C.c_char_p, [C.c_int]),
     "tfft_launch_count": (C.c_longlong, []),

@@ -166,6 +166,56 @@ __global__ void __launch_bounds__(256) scatter_transpose_kernel(const C* __restr
     }
 }
 
+// The same exchange for complex64 with 16-byte stores: tiles of 64 rows x 32 columns, a lane
+// writes two consecutive rows of one receiver column as one float4, so a warp's store covers a
+// 512-byte run of the receiver's line (the 32-row form above writes 256-byte runs of 8-byte
+// elements, which the NVLink path moves at a lower rate).  Needs rows % 64 == 0 and receiver
+// lines that start on 16-byte boundaries.
+template <bool TW>
+__global__ void __launch_bounds__(256) scatter_transpose_wide_kernel(const float2* __restrict__ src, PeerPtrs<float2> dst,
+                                                                     long long rows, long long cols, long long cb,
+                                                                     long long row0, int log_total, int n_peers,
+                                                                     long long sub_off, long long sub_len) {
+    __shared__ __align__(16) float2 tile[32][66];  // [column][row]; pitch 66 keeps every tile row 16-byte aligned
+    const long long ts = sub_len / 32;
+    const long long n_tiles = (rows / 64) * ts * n_peers;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const long long tr = t / (ts * n_peers);
+        const long long rem = t % (ts * n_peers);
+        const long long c0 = (rem / ts) * cb + sub_off + (rem % ts) * 32;
+        const long long c = c0 + tx;
+        float2 w, step;
+        if (TW) {
+            const unsigned long long mask = (1ULL << log_total) - 1;
+            w = unit_twiddle(((unsigned long long)(row0 + tr * 64 + ty) * (unsigned long long)c) & mask, log_total, 0.0f);
+            step = unit_twiddle((8ULL * (unsigned long long)c) & mask, log_total, 0.0f);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const long long r = tr * 64 + ty + 8 * k;
+            float2 v = __ldcs(src + r * cols + c);
+            if (TW) {
+                const float2 u = make_float2(v.x * w.x - v.y * w.y, v.x * w.y + v.y * w.x);
+                v = u;
+                if (k < 7) w = make_float2(w.x * step.x - w.y * step.y, w.x * step.y + w.y * step.x);
+            }
+            tile[tx][ty + 8 * k] = v;
+        }
+        __syncthreads();
+        const int j = (int)(c0 / cb);
+        float2* base = dst.p[j] + dst.roff[j] + tr * 64;
+        const long long ld = dst.ld[j];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const long long cc = c0 + ty + 8 * k;
+            const float4 v = *reinterpret_cast<const float4*>(&tile[ty + 8 * k][2 * tx]);
+            reinterpret_cast<float4*>(base + (cc % cb) * ld)[tx] = v;
+        }
+        __syncthreads();
+    }
+}
+
 template <bool TW>
 int launch_transpose(const void* src, void* dst, long long rows, long long cols, long long row0, long long col0,
                      int log_total, int dtype, void* stream) {
@@ -232,12 +282,22 @@ int tfft_scatter_transpose_ex(const void* src, void* const* dst, const long long
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == TFFT_FLOAT2) {
         PeerPtrs<float2> pp;
+        bool wide = (rows & 63) == 0;
         for (int i = 0; i < kMaxPeers; ++i) {
             pp.p[i] = (float2*)(i < n_peers ? dst[i] : nullptr);
             pp.ld[i] = i < n_peers ? dst_ld[i] : 0;
             pp.roff[i] = i < n_peers ? dst_row0[i] : 0;
+            if (i < n_peers && (((size_t)dst[i] & 15) || (dst_ld[i] & 1) || (dst_row0[i] & 1))) wide = false;
         }
-        if (twiddle)
+        if (wide) {
+            long long wblocks = (rows / 64) * (sub_len / 32) * n_peers;
+            if (max_blocks > 0 && wblocks > max_blocks) wblocks = max_blocks;
+            if (wblocks > 2147483647LL) wblocks = 2147483647LL;
+            if (twiddle)
+                scatter_transpose_wide_kernel<true><<<(unsigned)wblocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
+            else
+                scatter_transpose_wide_kernel<false><<<(unsigned)wblocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
+        } else if (twiddle)
             scatter_transpose_kernel<float2, true><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);
         else
             scatter_transpose_kernel<float2, false><<<(unsigned)blocks, 256, 0, st>>>((const float2*)src, pp, rows, cols, cb, tw_row0, log_total, n_peers, sub_off, sub_len);

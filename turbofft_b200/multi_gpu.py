@@ -455,3 +455,40 @@ class FusedFourStepFFT(FourStepFFT):
 
     def close(self):
         self.bufs.close()
+
+
+class SingleProcessFourStep:
+    """The same transform driven from ONE process over several devices (C ABI tfft_mg_*): rank r
+    is position r of `devices`; a device may be listed more than once.  x_parts / results are
+    lists of per-rank CUDA tensors of N / len(devices) elements."""
+
+    def __init__(self, logn: int, dtype_code: int, devices, natural_order: bool = False, if_ft: int = 0, pipeline: int = 1):
+        self.logn, self.dt, self.devices = logn, dtype_code, list(devices)
+        self.l1, self.l2 = split_log(logn)
+        self._h = C.c_void_p()
+        arr = (C.c_int * len(self.devices))(*self.devices)
+        _lib.check(lib().tfft_mg_plan_create(C.byref(self._h), logn, dtype_code, int(if_ft), len(self.devices), arr,
+                                             int(natural_order), int(pipeline)), "tfft_mg_plan_create")
+
+    def __call__(self, x_parts):
+        import torch
+
+        P = len(self.devices)
+        outs = [torch.empty_like(x) for x in x_parts]
+        for x in x_parts:                      # inputs were produced on torch's streams
+            torch.cuda.synchronize(x.device)
+        ins = (C.c_void_p * P)(*[x.data_ptr() for x in x_parts])
+        ous = (C.c_void_p * P)(*[y.data_ptr() for y in outs])
+        _lib.check(lib().tfft_mg_exec(self._h, ins, ous, None), "tfft_mg_exec")
+        _lib.check(lib().tfft_mg_sync(self._h), "tfft_mg_sync")
+        return outs
+
+    def ft_counts(self):
+        nd, nc = C.c_int(), C.c_int()
+        _lib.check(lib().tfft_mg_ft_status(self._h, C.byref(nd), C.byref(nc)), "tfft_mg_ft_status")
+        return nd.value, nc.value
+
+    def close(self):
+        if self._h:
+            lib().tfft_mg_destroy(self._h)
+            self._h = C.c_void_p()
