@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--cufft", action="store_true", help="also time cuFFT on the same buffers (comparison only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--param-csv", default=None, help="plans from this parameter file instead of the built-in tables")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary measurements of the 'also' object")
     ap.add_argument("--also-steps", type=int, default=3)
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -455,7 +456,7 @@ def run_ours(a):
     plans = {}
     for logn in points:
         plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2),
-                              thread_bs=a.thread_bs, device=local)
+                              thread_bs=a.thread_bs, device=local, param_csv=a.param_csv)
     stream = torch.cuda.current_stream().cuda_stream
 
     def step(events=None):

@@ -64,6 +64,16 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
  * 16 bytes; in == out is allowed. */
 int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int dtype, int log_cluster,
                                  int thread_bs, int device);
+/* Strided batch: the array is [outer][N][inner] (row-major, contiguous) and the transform runs
+ * along the middle axis -- lines of N = 2^logN points strided by `inner` (a power of two),
+ * outer * inner of them: the batch as an extra dimension, as the reference's small-N kernels
+ * treat it (fft_codegen.py:756-762), and what a 2-D transform needs for its column pass.  One
+ * launch of the strided-line kernel a multi-launch plan uses for its first launch, without the
+ * inter-launch twiddle; tiles are adjacent columns, so rows are read and written in runs of up
+ * to 32 elements.  Lengths: those with a compiled strided-line kernel (2^1..2^12 in the shipped
+ * build), else TFFT_ERR_UNSUPPORTED.  FT off.  in == out is allowed.  tfft_set_direction
+ * applies. */
+int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long long outer, int dtype, int device);
 /* CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches. */
 int tfft_plan_cluster_size(tfft_plan plan);
 
@@ -75,6 +85,17 @@ int tfft_plan_cluster_size(tfft_plan plan);
  * is recomputed from the input; see tfft_set_correction for the way around).  `stream` is a cudaStream_t (NULL = default).
  * Stream ordered; returns without synchronising. */
 int tfft_exec(tfft_plan plan, const void* in, void* out, void* stream);
+
+/* The same launches with the intermediate buffer supplied by the caller, so that ONE plan can be
+ * executed from several host threads on several streams at the same time (tfft_exec keeps the
+ * intermediate result of multi-launch plans in a buffer the plan owns, which two overlapping
+ * execs would share).  workspace: tfft_scratch_bytes(plan) bytes of device memory, 256-byte
+ * aligned, private to this exec until it has completed (NULL when that is 0: one-launch and
+ * single-pass plans).  Plans without FT only (the FT status buffers are per plan):
+ * TFFT_ERR_UNSUPPORTED otherwise.  The reference's launcher is single-threaded and
+ * synchronises after every launch (main.cu:58); it has nothing to share. */
+size_t tfft_scratch_bytes(tfft_plan plan);
+int tfft_exec_ws(tfft_plan plan, const void* in, void* out, void* workspace, void* stream);
 
 /* Same transform with HOST buffers: copies batch*N elements to the device, runs
  * tfft_exec and copies the result back, then synchronises.  Replaces the

@@ -225,3 +225,67 @@ def test_thread_bs_zero_follows_the_tuned_table(torch_cuda):
     assert plan.info()[0]["grid"] == -(-batch // want)          # one signal per tile at this size
     y = plan(torch_cuda.from_numpy(x).cuda()).cpu().numpy()
     assert orc.rel_l2(y, orc.fft_forward(x)) <= orc.tolerance(np.complex64, logn)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("shape,dim", [((3, 256, 64), 1), ((1, 1024, 8), -2), ((5, 128, 2, 16), 1), ((512, 32), 0), ((2, 64, 4), 1),
+                                       ((7, 2, 32), 1), ((3, 16, 1), 1), ((2, 4096, 2), 1), ((1, 2048, 64), 1)])
+def test_strided_batch_along_a_middle_axis(torch_cuda, shape, dim, dtype):
+    """tfft_plan_create_strided: lines strided by the product of the trailing axes, no copy."""
+    import turbofft_b200 as tf
+
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal(shape) + 1j * rng.standard_normal(shape)).astype(CD[dtype])
+    xd = torch_cuda.from_numpy(x).cuda()
+    y = tf.fft(xd, dim=dim).cpu().numpy()
+    ref = np.fft.fft(x.astype(np.complex128), axis=dim)
+    logn = int(np.log2(shape[dim]))
+    assert orc.rel_l2(y, ref) <= orc.tolerance(CD[dtype], logn)
+    back = tf.ifft(tf.fft(xd, dim=dim), dim=dim).cpu().numpy()
+    assert orc.rel_l2(back, x) <= 2 * orc.tolerance(CD[dtype], logn)
+
+
+def test_two_dimensional_transform(torch_cuda):
+    import turbofft_b200 as tf
+
+    rng = np.random.default_rng(12)
+    x = (rng.uniform(-1, 1, (3, 256, 512)) + 1j * rng.uniform(-1, 1, (3, 256, 512))).astype(np.complex64)
+    y = tf.fft2(torch_cuda.from_numpy(x).cuda()).cpu().numpy()
+    assert orc.rel_l2(y, np.fft.fft2(x.astype(np.complex128))) <= orc.tolerance(np.complex64, 17)
+
+
+def test_strided_plan_refuses_what_it_cannot_do(torch_cuda):
+    import ctypes as C
+
+    import turbofft_b200 as tf
+
+    h = C.c_void_p()
+    lib = tf.lib()
+    assert lib.tfft_plan_create_strided(C.byref(h), 8, 48, 2, 0, 0) == -1       # inner not a power of two
+    assert lib.tfft_plan_create_strided(C.byref(h), 20, 16, 2, 0, 0) == -2      # no strided-line kernel of that length
+
+
+def test_one_plan_on_two_streams_with_caller_workspaces(torch_cuda):
+    """tfft_exec_ws: the same multi-launch plan runs on two streams at once, each exec with its own
+    intermediate buffer; both results equal the plan's ordinary exec."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    lib = tf.lib()
+    logn, batch = 18, 16
+    plan = tf.Plan(logn, batch, 0)
+    nbytes = lib.tfft_scratch_bytes(plan._h)
+    assert nbytes == (batch << logn) * 8
+    xs = [torch.from_numpy(orc.make_input(batch, 1 << logn, np.complex64, seed=s)).cuda() for s in (1, 2)]
+    want = [plan(x).clone() for x in xs]
+    ws = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in xs]
+    ys = [torch.empty_like(x) for x in xs]
+    streams = [torch.cuda.Stream() for _ in xs]
+    torch.cuda.synchronize()
+    for _ in range(5):
+        for x, y, w, s in zip(xs, ys, ws, streams):
+            assert lib.tfft_exec_ws(plan._h, x.data_ptr(), y.data_ptr(), w.data_ptr(), s.cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert all(torch.equal(y, w_) for y, w_ in zip(ys, want))
+    ft = tf.Plan(logn, batch, 0, if_ft=1)
+    assert lib.tfft_exec_ws(ft._h, xs[0].data_ptr(), ys[0].data_ptr(), ws[0].data_ptr(), 0) == -2

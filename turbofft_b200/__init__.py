@@ -165,16 +165,55 @@ _plan_cache = {}
 _NORM_FWD = {None: 0.0, "backward": 0.0, "ortho": -0.5, "forward": -1.0}  # exponent of N in the forward scale
 
 
-def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None, inverse: bool = False):
-    """FFT along the last axis of a complex64/complex128 CUDA tensor (forward, unnormalised by
+def _fft_strided(x, dim: int, norm, inverse: bool):
+    """Transform along a middle axis of a contiguous tensor: [outer][N][inner], lines strided by inner."""
+    torch = _torch()
+    x = x.contiguous()
+    n = x.shape[dim]
+    logn = n.bit_length() - 1
+    inner = 1
+    for s in x.shape[dim + 1:]:
+        inner *= s
+    outer = x.numel() // (n * inner)
+    if n < 2 or (1 << logn) != n or inner & (inner - 1):
+        raise ValueError("the transformed axis and the product of the axes behind it must be powers of two")
+    expo = _NORM_FWD[norm] if not inverse else -1.0 - _NORM_FWD[norm]
+    key = ("strided", x.device.index, logn, inner, outer, _dtype_code(x.dtype), bool(inverse), expo)
+    plan = _plan_cache.get(key)
+    if plan is None:
+        plan = Plan.__new__(Plan)
+        plan._h = C.c_void_p()
+        plan.logN, plan.batch, plan.dtype, plan.device = logn, outer * inner, _dtype_code(x.dtype), x.device.index
+        plan.if_ft = plan.if_err = 0
+        plan.thread_bs = 1
+        _lib.check(lib().tfft_plan_create_strided(C.byref(plan._h), logn, inner, outer, plan.dtype, plan.device),
+                   f"tfft_plan_create_strided(logN={logn}, inner={inner}, outer={outer})")
+        plan.set_direction(inverse, float(n) ** expo)
+        _plan_cache[key] = plan
+    y = torch.empty_like(x)
+    plan.exec_ptr(x.data_ptr(), y.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    return y
+
+
+def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None, inverse: bool = False, dim: int = -1):
+    """FFT along one axis of a complex64/complex128 CUDA tensor (forward, unnormalised by
     default, which is the reference's transform).
 
-    Power-of-two lengths 2..2^30; leading axes are the batch.  ft/err are the
-    reference's --if_ft / --if_err.  norm follows torch.fft ("backward", "ortho", "forward");
-    inverse=True is what ifft() calls.  Plans are cached per (device, shape, mode).
+    Power-of-two lengths 2..2^30 along the last axis; leading axes are the batch.  ft/err are
+    the reference's --if_ft / --if_err.  norm follows torch.fft ("backward", "ortho", "forward");
+    inverse=True is what ifft() calls.  dim other than the last axis runs the strided-batch plan
+    (no copy, no transpose; lengths with a compiled strided-line kernel, FT off).  Plans are
+    cached per (device, shape, mode).
     """
     if not x.is_cuda:
         raise ValueError("turbofft_b200.fft needs a CUDA tensor: there is no CPU path")
+    if norm not in _NORM_FWD:
+        raise ValueError(f"unknown norm {norm!r}")
+    dim = dim % x.dim()
+    if dim != x.dim() - 1:
+        if ft or err or out is not None:
+            raise ValueError("the strided-batch plan has no FT mode and allocates its output")
+        return _fft_strided(x, dim, norm, inverse)
     n = x.shape[-1]
     logn = n.bit_length() - 1
     if n < 2 or (1 << logn) != n:
@@ -193,9 +232,15 @@ def fft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, no
     return y.reshape(x.shape)
 
 
-def ifft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None):
-    """Inverse FFT along the last axis (1/N scaling by default, as torch.fft.ifft)."""
-    return fft(x, ft=ft, err=err, thread_bs=thread_bs, out=out, norm=norm, inverse=True)
+def ifft(x, ft: bool = False, err: bool = False, thread_bs: int = 1, out=None, norm=None, dim: int = -1):
+    """Inverse FFT along one axis (1/N scaling by default, as torch.fft.ifft)."""
+    return fft(x, ft=ft, err=err, thread_bs=thread_bs, out=out, norm=norm, inverse=True, dim=dim)
+
+
+def fft2(x, norm=None, inverse: bool = False):
+    """2-D transform over the last two axes: the strided-batch plan along the rows' axis, then the
+    ordinary plan along the last axis (both lengths powers of two)."""
+    return fft(fft(x, dim=-2, norm=norm, inverse=inverse), norm=norm, inverse=inverse)
 
 
 def stream_copy(src, dst) -> None:

@@ -117,6 +117,7 @@ struct tfft_plan_s {
     int diag = 0;
     int ft_accumulate = 0;  // 1: the FT counters add up over execs until tfft_ft_status reads (and clears) them
     int csum = 0;        // 1: repair from the running checksums (FT_CSUM kernels) where they exist
+    int strided = 0;     // 1: one ROLE_FIRST launch on its own, lines strided by 2^L[0].log_b (tfft_plan_create_strided)
     int inverse = 0;     // 0: forward; 1: conjugate in, conjugate out (inverse transform)
     double scale = 1.0;  // applied with the conjugation of the last launch
     cudaStream_t last_stream = nullptr;
@@ -276,7 +277,7 @@ bool build_tables(tfft_plan p) {
                 if (!upload(p, c, &d.cks)) return false;
             }
         }
-        if (d.role == ROLE_FIRST) {
+        if (d.role == ROLE_FIRST && !p->strided) {
             const int logp = d.logm + d.log_b;
             d.tw_lo_bits = (logp + 1) / 2;
             std::vector<C> lo, hi;
@@ -330,7 +331,7 @@ int launch_cluster(tfft_plan p, const void* in, void* out, cudaStream_t st) {
 }
 
 template <typename T>
-int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
+int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st, void* scratch) {
     typedef typename Cplx<T>::type C;
     if (p->ck) return launch_cluster<T>(p, in, out, st);
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
@@ -347,8 +348,8 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         // input, so no launch may overwrite what it reads: its middle launch goes scratch ->
         // scratch2 (the reference alternates two buffers for every launch, main.cu:11-12).
         const bool pingpong = p->scratch2 != nullptr;
-        a.in = (const C*)(i == 0 ? in : (i == 2 && pingpong ? p->scratch2 : p->scratch));
-        a.out = (C*)(i == p->n_launch - 1 ? out : (i == 1 && pingpong ? p->scratch2 : p->scratch));
+        a.in = (const C*)(i == 0 ? in : (i == 2 && pingpong ? p->scratch2 : scratch));
+        a.out = (C*)(i == p->n_launch - 1 ? out : (i == 1 && pingpong ? p->scratch2 : scratch));
         a.tw_st = (const C*)d.tw_st;
         a.tw_lo = (const C*)d.tw_lo;
         a.tw_hi = (const C*)d.tw_hi;
@@ -361,6 +362,7 @@ int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st) {
         a.log_n1 = d.log_n1;
         a.log_q = d.log_q;
         a.tw_lo_bits = d.tw_lo_bits;
+        a.no_twiddle = p->strided;
         a.conj_in = (p->inverse && i == 0) ? 1 : 0;
         a.scale_out = ((p->inverse || p->scale != 1.0) && i == p->n_launch - 1) ? 1 : 0;
         a.scale_x = (T)p->scale;
@@ -556,6 +558,72 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
     return TFFT_OK;
 }
 
+int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long long outer, int dtype, int device) {
+    if (!plan) return TFFT_ERR_BAD_ARG;
+    *plan = nullptr;
+    const int log_b = ilog2_exact(inner);
+    if (logN < 1 || logN > 30 || inner < 1 || log_b < 0 || outer < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || device < 0)
+        return TFFT_ERR_BAD_ARG;
+    // the widest compiled strided-line kernel for this length whose tile fits the inner extent
+    const KernelEntry* k = nullptr;
+    int logc = 0, loge = 0;
+    for (int c = 5; c >= 0 && !k; --c) {
+        if (c > log_b) continue;
+        for (int e = 5; e >= 1 && !k; --e) {
+            const KernelEntry* q = find_kernel(dtype, ROLE_FIRST, logN, e, c);
+            if (q && q->fn[FT_OFF]) {
+                k = q;
+                logc = c;
+                loge = e;
+            }
+        }
+    }
+    if (!k) return TFFT_ERR_UNSUPPORTED;
+    const long long tiles = outer << (log_b - logc);
+    if (tiles > 2147483647LL || (outer << log_b) > (1LL << (62 - logN))) return TFFT_ERR_TOO_LARGE;
+    DeviceGuard guard(device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    tfft_plan p = new (std::nothrow) tfft_plan_s();
+    if (!p) return TFFT_ERR_ALLOC;
+    p->logn = logN;
+    p->batch = outer << log_b;
+    p->dtype = dtype;
+    p->device = device;
+    p->n_launch = 1;
+    p->strided = 1;
+    LaunchDesc& d = p->L[0];
+    d.role = ROLE_FIRST;
+    d.logm = logN;
+    d.loge = loge;
+    d.logc = logc;
+    d.log_b = log_b;
+    d.n_tiles = tiles;
+    d.grid = (unsigned)tiles;
+    d.k = k;
+    snprintf(p->nvtx_name, sizeof(p->nvtx_name), "tfft_exec logN=%d strided inner=%lld outer=%lld", logN, inner, outer);
+    int status = TFFT_OK;
+    if (k->smem > 40 * 1024 &&
+        !cuda_ok(p, cudaFuncSetAttribute(k->fn[FT_OFF], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem)))
+        status = TFFT_ERR_CUDA;
+    if (status == TFFT_OK) {
+        const bool okb = dtype == TFFT_FLOAT2 ? build_tables<float>(p) : build_tables<double>(p);
+        if (!okb) status = p->last_cuda_error ? TFFT_ERR_CUDA : TFFT_ERR_ALLOC;
+    }
+#if TFFT_BOUNDS_CHECK
+    if (status == TFFT_OK) {
+        p->oob = (unsigned long long*)dev_alloc(p, sizeof(unsigned long long));
+        if (!p->oob || !cuda_ok(p, cudaMemset(p->oob, 0, sizeof(unsigned long long)))) status = TFFT_ERR_ALLOC;
+    }
+#endif
+    if (status != TFFT_OK) {
+        for (void* q : p->allocs) cudaFree(q);
+        delete p;
+        return status;
+    }
+    *plan = p;
+    return TFFT_OK;
+}
+
 int tfft_plan_cluster_size(tfft_plan p) { return p ? (p->ck ? (1 << p->ck->logg) : 0) : TFFT_ERR_BAD_ARG; }
 
 int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
@@ -566,7 +634,23 @@ int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     p->last_stream = st;
     NvtxRange range(p->nvtx_name);
-    return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st) : launch_all<double>(p, in, out, st);
+    return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st, p->scratch) : launch_all<double>(p, in, out, st, p->scratch);
+}
+
+size_t tfft_scratch_bytes(tfft_plan p) {
+    if (!p || p->n_launch < 2 || p->ck) return 0;
+    return ((size_t)p->batch << p->logn) * p->esize();
+}
+
+int tfft_exec_ws(tfft_plan p, const void* in, void* out, void* workspace, void* stream) {
+    if (!p || !in || !out) return TFFT_ERR_BAD_ARG;
+    if (p->if_ft) return TFFT_ERR_UNSUPPORTED;  // the FT status buffers belong to the plan: one exec at a time
+    if (tfft_scratch_bytes(p) && !workspace) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    NvtxRange range(p->nvtx_name);
+    return p->dtype == TFFT_FLOAT2 ? launch_all<float>(p, in, out, st, workspace) : launch_all<double>(p, in, out, st, workspace);
 }
 
 // Pipelined form of tfft_exec_host for plans without FT whose batch spans several chunks:

@@ -75,6 +75,7 @@ struct KernelArgs {
     int inj_on;         // add err_inj to one element of one tile per selected block
     int inj_period;     // blocks b with b % inj_period == inj_phase are hit
     int inj_phase;
+    int no_twiddle;     // ROLE_FIRST used on its own (strided batch): no inter-launch twiddle
     int conj_in;        // conjugate while loading (first launch of an inverse transform)
     int scale_out;      // scale while storing (last launch): y = (y.x * scale_x, y.y * scale_y);
     T scale_x;          // inverse transform: (s, -s) conjugates and scales; forward with a norm: (s, s)
@@ -407,7 +408,7 @@ struct Fft {
                 else y[i] = csub(acc, y[i]);  // the error this block's outputs carry at this position
             }
         }
-        if (ROLE == ROLE_FIRST) {
+        if (ROLE == ROLE_FIRST && !a.no_twiddle) {
             // y_k *= W_P^{col*k}, k = s + i*TPL, i.e. base * step^i
             const unsigned long long col = (unsigned long long)(g.col0 + c);
             const unsigned long long pmask = (1ULL << (LOGM + a.log_b)) - 1;
