@@ -64,6 +64,13 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
  * 16 bytes; in == out is allowed. */
 int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int dtype, int log_cluster,
                                  int thread_bs, int device);
+/* OR-ed into log_cluster: the variant whose CTAs fetch their share of the NEXT signal into a
+ * second shared-memory buffer with bulk asynchronous copies completing on an mbarrier while the
+ * current signal is transformed (thread_bs > 1 gives it something to fetch ahead).  Its wait for
+ * that buffer is bounded; tfft_plan_device_status reports 1 if a wait ever gave up (the output
+ * of that exec is then invalid), 0 otherwise (synchronises with the device). */
+#define TFFT_SINGLE_PASS_PREFETCH 16
+int tfft_plan_device_status(tfft_plan plan, int* status);
 /* Strided batch: the array is [outer][N][inner] (row-major, contiguous) and the transform runs
  * along the middle axis -- lines of N = 2^logN points strided by `inner` (a power of two),
  * outer * inner of them: the batch as an extra dimension, as the reference's small-N kernels

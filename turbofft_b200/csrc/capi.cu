@@ -104,6 +104,7 @@ struct tfft_plan_s {
     void* ctw0 = nullptr;
     void* ctwp[4] = {nullptr, nullptr, nullptr, nullptr};
     unsigned cgrid_clusters = 0;
+    int* cstatus = nullptr;  // prefetching single-pass kernels: device word, 1 = a bounded wait gave up
     void* scratch = nullptr;
     void* scratch2 = nullptr;          // 3-launch plans that correct: the middle launch writes here, so that
                                        // its own input survives for the recompute of a located tile
@@ -325,6 +326,7 @@ int launch_cluster(tfft_plan p, const void* in, void* out, cudaStream_t st) {
     a.scale_out = (p->inverse || p->scale != 1.0) ? 1 : 0;
     a.scale_x = (T)p->scale;
     a.scale_y = (T)(p->inverse ? -p->scale : p->scale);
+    a.status = p->cstatus;
     if (!cuda_ok(p, launch_cluster_kernel(*p->ck, &a, p->cgrid_clusters, st))) return TFFT_ERR_CUDA;
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return TFFT_OK;
@@ -528,7 +530,9 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
     *plan = nullptr;
     if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 1 || device < 0)
         return TFFT_ERR_BAD_ARG;
-    const ClusterKernel* ck = find_cluster_kernel(dtype, logN, log_cluster);
+    const int prefetch = log_cluster >= 0 && (log_cluster & TFFT_SINGLE_PASS_PREFETCH) ? 1 : 0;
+    if (log_cluster >= 0) log_cluster &= ~TFFT_SINGLE_PASS_PREFETCH;
+    const ClusterKernel* ck = find_cluster_kernel(dtype, logN, log_cluster, prefetch);
     if (!ck) return TFFT_ERR_UNSUPPORTED;
     DeviceGuard guard(device);
     if (!guard.ok) return TFFT_ERR_CUDA;
@@ -547,7 +551,11 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
     p->cgrid_clusters = (unsigned)clusters;
     snprintf(p->nvtx_name, sizeof(p->nvtx_name), "tfft_exec logN=%d batch=%lld %s single-pass", logN, batch,
              dtype == TFFT_FLOAT2 ? "c64" : "c128");
-    const bool ok = dtype == TFFT_FLOAT2 ? build_cluster_tables<float>(p) : build_cluster_tables<double>(p);
+    bool ok = dtype == TFFT_FLOAT2 ? build_cluster_tables<float>(p) : build_cluster_tables<double>(p);
+    if (ok && ck->prefetch) {
+        p->cstatus = (int*)dev_alloc(p, sizeof(int));
+        ok = p->cstatus && cuda_ok(p, cudaMemset(p->cstatus, 0, sizeof(int)));
+    }
     if (!ok) {
         const int status = p->last_cuda_error ? TFFT_ERR_CUDA : TFFT_ERR_ALLOC;
         for (void* q : p->allocs) cudaFree(q);
@@ -621,6 +629,16 @@ int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long lo
         return status;
     }
     *plan = p;
+    return TFFT_OK;
+}
+
+int tfft_plan_device_status(tfft_plan p, int* status) {
+    if (!p || !status) return TFFT_ERR_BAD_ARG;
+    *status = 0;
+    if (!p->cstatus) return TFFT_OK;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaMemcpy(status, p->cstatus, sizeof(int), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
     return TFFT_OK;
 }
 

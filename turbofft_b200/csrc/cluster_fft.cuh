@@ -116,12 +116,15 @@ struct ClusterCfg {
     static __host__ __device__ constexpr int pad(int l) { return l + (l >> 3) + (l >> 6); }
     static constexpr int UNITS = pad(R * TH - 1) + 1;
     static constexpr size_t SMEM_BYTES = (size_t)UNITS * 4 * sizeof(T);
+    // prefetching variant: behind the exchange buffer, a landing buffer for the CTA's share of the
+    // next signal (E * TH complex values) and the mbarrier its bulk copies complete on
+    static constexpr size_t SMEM_BYTES_PF = SMEM_BYTES + (size_t)E * TH * 2 * sizeof(T) + 16;
     // entries of the twiddle tables
     static constexpr size_t tw0_count() { return (size_t)LR0 << (LOGN - LR0); }
     static __host__ __device__ constexpr size_t twp_count(int t) { return ((size_t)LR << (LOGT - logp(t))) * 4; }  // in T
 };
 
-template <typename T, int LOGN, int LR0, int LOGG>
+template <typename T, int LOGN, int LR0, int LOGG, bool PF = false>
 struct ClusterFft {
     typedef ClusterCfg<T, LOGN, LR0, LOGG> K;
     typedef typename Cplx<T>::type C;  // one complex value, or one value per lane
@@ -202,17 +205,18 @@ struct ClusterFft {
         }
     }
 
-    // ---- stage 0: global -> registers -> radix R0 -> twiddle -> units in local shared memory
-    static __device__ __forceinline__ void stage0(const ClusterArgs<T>& a, T* sm, const C* src, int rank, int lid) {
-        constexpr int R0 = K::R0, NB0 = K::NB0;
-        const int s0 = join(0, rank, lid);
-        C v[E];
+    // ---- stage 0: registers <- global (or the landing buffer) ...
+    static __device__ __forceinline__ void stage0_load(const ClusterArgs<T>& a, C (&v)[E], const C* src, int first, int stride) {
 #pragma unroll
-        for (int i = 0; i < E; ++i) v[i] = src[s0 + i * K::T_];
+        for (int i = 0; i < E; ++i) v[i] = src[first + i * stride];
         if (a.conj_in) {
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].y = -v[i].y;
         }
+    }
+    // ... -> radix R0 -> twiddle -> units in local shared memory
+    static __device__ __forceinline__ void stage0_compute(const ClusterArgs<T>& a, T* sm, C (&v)[E], int s0) {
+        constexpr int R0 = K::R0, NB0 = K::NB0;
 #pragma unroll
         for (int u = 0; u < NB0; ++u) dif_butterfly<LR0, NB0, T>(v, u);
         // unit m = (q >> 1) + (R0 / 2) * b with b = s0 + u * T: thread part, u part, q part
@@ -240,6 +244,46 @@ struct ClusterFft {
                 store_unit(sm, base + local_index(1, (q >> 1) + (R0 / 2) * u * K::T_), un);
             }
         }
+    }
+
+    // ---- prefetch of a signal's share into the landing buffer: bulk copies completing on an mbarrier
+    static __device__ __forceinline__ void bar_init(uint64_t* bar) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)) : "memory");
+    }
+    static __device__ __forceinline__ void prefetch(const ClusterArgs<T>& a, C* land, uint64_t* bar, const C* src, int rank) {
+        constexpr int RP0 = K::rank_pos(0);
+        constexpr int RUN = 1 << RP0;                  // contiguous elements of this CTA per (i, run) in global memory
+        constexpr int RUNS_PER_I = TH >> RP0;
+        constexpr int NRUN = E * RUNS_PER_I;
+        constexpr uint32_t RUN_BYTES = RUN * (uint32_t)sizeof(C);
+        static_assert(RUN_BYTES % 16 == 0, "bulk copies move multiples of 16 bytes");
+        const uint32_t bar_s = smem_u32(bar);
+        if (threadIdx.x == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_s), "r"((uint32_t)(E * TH * sizeof(C)))
+                         : "memory");
+        for (int r = threadIdx.x; r < NRUN; r += TH) {
+            const int i = r / RUNS_PER_I, lh = r % RUNS_PER_I;
+            const C* g = src + join(0, rank, lh << RP0) + (size_t)i * K::T_;
+            const uint32_t dst = smem_u32(land + i * TH + (lh << RP0));
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                         "l"(g), "r"(RUN_BYTES), "r"(bar_s)
+                         : "memory");
+        }
+    }
+    // Bounded wait for the landing buffer: gives up after a long time, records it and goes on (the
+    // result is then wrong, the host sees the status word; the kernel never hangs).
+    static __device__ __forceinline__ void bar_wait(const ClusterArgs<T>& a, uint64_t* bar, uint32_t parity) {
+        const uint32_t bar_s = smem_u32(bar);
+        for (int spin = 0; spin < (1 << 22); ++spin) {
+            uint32_t done;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(bar_s), "r"(parity)
+                : "memory");
+            if (done) return;
+        }
+        if (a.status) atomicExch(a.status, 1);
     }
 
     // ---- unit stage ST (1 .. S2): read R units, butterflies, then twiddle + exchange or store
@@ -370,10 +414,33 @@ struct ClusterFft {
         const int rank = cluster_rank();
         const int lid = threadIdx.x;
         const long long cluster_id = blockIdx.x >> LOGG, n_clusters = gridDim.x >> LOGG;
+        const int s0 = join(0, rank, lid);
+        C* land = reinterpret_cast<C*>(sm + 4 * (size_t)K::UNITS);
+        uint64_t* bar = reinterpret_cast<uint64_t*>(land + E * TH);
+        uint32_t parity = 0;
+        if constexpr (PF) {
+            if (threadIdx.x == 0) bar_init(bar);
+            __syncthreads();
+            if (cluster_id < a.n_signals && a.signals_per_cluster > 0) prefetch(a, land, bar, a.in + (cluster_id << LOGN), rank);
+        }
         for (int it = 0; it < a.signals_per_cluster; ++it) {
             const long long sig = cluster_id + it * n_clusters;
             if (sig >= a.n_signals) break;  // the same decision in every CTA of the cluster
-            stage0(a, sm, a.in + (sig << LOGN), rank, lid);
+            C v[E];
+            if constexpr (PF) {
+                bar_wait(a, bar, parity);
+                parity ^= 1u;
+                stage0_load(a, v, land, lid, TH);
+                __syncthreads();  // everybody has its values: the landing buffer is free for the next signal
+                const long long next = sig + n_clusters;
+                if (it + 1 < a.signals_per_cluster && next < a.n_signals) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    prefetch(a, land, bar, a.in + (next << LOGN), rank);
+                }
+            } else {
+                stage0_load(a, v, a.in + (sig << LOGN), s0, K::T_);
+            }
+            stage0_compute(a, sm, v, s0);
             __syncthreads();
             // (the last stage ends with a barrier behind its reads, so the next signal's stage 0
             // may overwrite shared memory at once)
@@ -382,11 +449,11 @@ struct ClusterFft {
     }
 };
 
-template <typename T, int LOGN, int LR0, int LOGG>
-__global__ void __launch_bounds__((ClusterCfg<T, LOGN, LR0, LOGG>::TH), (512 / ClusterCfg<T, LOGN, LR0, LOGG>::TH))
+template <typename T, int LOGN, int LR0, int LOGG, bool PF>
+__global__ void __launch_bounds__((ClusterCfg<T, LOGN, LR0, LOGG>::TH), (PF ? 384 : 512) / ClusterCfg<T, LOGN, LR0, LOGG>::TH)
 cluster_fft_kernel(const __grid_constant__ ClusterArgs<T> a) {
     extern __shared__ __align__(16) unsigned char tfft_cluster_smem[];
-    ClusterFft<T, LOGN, LR0, LOGG>::run(a, reinterpret_cast<T*>(tfft_cluster_smem));
+    ClusterFft<T, LOGN, LR0, LOGG, PF>::run(a, reinterpret_cast<T*>(tfft_cluster_smem));
 }
 
 }  // namespace tfft

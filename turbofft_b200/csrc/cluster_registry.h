@@ -24,18 +24,20 @@ struct ClusterArgs {
     int conj_in;    // conjugate while loading (inverse transform)
     int scale_out;  // scale while storing: y = (y.x * scale_x, y.y * scale_y)
     T scale_x, scale_y;
+    int* status;  // prefetching variant: set to 1 if a wait for the landing buffer ever gave up
 };
 
 struct ClusterKernel {
     const void* fn = nullptr;
     int dtype = 0, logn = 0, lr0 = 0, lr = 0, logg = 0, s2 = 0;
+    int prefetch = 0;  // 1: the next signal's input is fetched into shared memory by bulk copies while this one is transformed
     int threads = 0;
     size_t smem = 0;
 };
 
 void register_cluster_kernel(const ClusterKernel& k);
 // logg < 0: the first registered cluster size for (dtype, logn)
-const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg);
+const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg, int prefetch);
 int registered_cluster_kernel_count();
 
 // Host images of the kernel's twiddle tables (ClusterArgs::tw0 / twp), as raw element arrays of
