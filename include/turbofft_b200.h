@@ -70,6 +70,9 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
  * that buffer is bounded; tfft_plan_device_status reports 1 if a wait ever gave up (the output
  * of that exec is then invalid), 0 otherwise (synchronises with the device). */
 #define TFFT_SINGLE_PASS_PREFETCH 16
+/* OR-ed into log_cluster (complex64): the variant whose threads hold 16 points instead of 32
+ * (radix-8 stages), with half the registers per thread and twice the resident warps. */
+#define TFFT_SINGLE_PASS_RADIX8 32
 int tfft_plan_device_status(tfft_plan plan, int* status);
 /* Strided batch: the array is [outer][N][inner] (row-major, contiguous) and the transform runs
  * along the middle axis -- lines of N = 2^logN points strided by `inner` (a power of two),

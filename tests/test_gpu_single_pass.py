@@ -109,3 +109,19 @@ def test_prefetching_variant_matches_oracle(torch_cuda, logn, log_cluster):
         assert lib.tfft_plan_device_status(plan._h, C.byref(st)) == 0 and st.value == 0
         assert torch.equal(y, plain)
         assert orc.rel_l2(y.cpu().numpy(), orc.fft_forward(x)) <= orc.tolerance(np.complex64, logn)
+
+
+@pytest.mark.parametrize("logn,log_cluster", [(13, 1), (14, 2), (15, 3), (15, 4), (16, 4)])
+def test_radix8_variant_matches_oracle(torch_cuda, logn, log_cluster):
+    """TFFT_SINGLE_PASS_RADIX8: complex64 with 16 points per thread (radix-8 unit stages, one more
+    stage), half the registers and twice the resident warps."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    for batch, tbs in ((1, 1), (11, 3)):
+        x = orc.make_input(batch, 1 << logn, np.complex64, seed=batch + logn)
+        plan = tf.Plan(logn, batch, 0, single_pass=log_cluster | 32, thread_bs=tbs)
+        assert plan.cluster_size == 1 << log_cluster and plan.info()[0]["points_per_thread"] == 16
+        y = plan(torch.from_numpy(x).cuda())
+        torch.cuda.synchronize()
+        assert orc.rel_l2(y.cpu().numpy(), orc.fft_forward(x)) <= orc.tolerance(np.complex64, logn)

@@ -530,9 +530,12 @@ int tfft_plan_create_single_pass(tfft_plan* plan, int logN, long long batch, int
     *plan = nullptr;
     if (logN < 1 || logN > 30 || batch < 1 || (dtype != TFFT_FLOAT2 && dtype != TFFT_DOUBLE2) || thread_bs < 1 || device < 0)
         return TFFT_ERR_BAD_ARG;
-    const int prefetch = log_cluster >= 0 && (log_cluster & TFFT_SINGLE_PASS_PREFETCH) ? 1 : 0;
-    if (log_cluster >= 0) log_cluster &= ~TFFT_SINGLE_PASS_PREFETCH;
-    const ClusterKernel* ck = find_cluster_kernel(dtype, logN, log_cluster, prefetch);
+    int flavour = 0;
+    if (log_cluster >= 0) {
+        flavour = ((log_cluster & TFFT_SINGLE_PASS_PREFETCH) ? 1 : 0) + ((log_cluster & TFFT_SINGLE_PASS_RADIX8) ? 2 : 0);
+        log_cluster &= ~(TFFT_SINGLE_PASS_PREFETCH | TFFT_SINGLE_PASS_RADIX8);
+    }
+    const ClusterKernel* ck = find_cluster_kernel(dtype, logN, log_cluster, flavour);
     if (!ck) return TFFT_ERR_UNSUPPORTED;
     DeviceGuard guard(device);
     if (!guard.ok) return TFFT_ERR_CUDA;

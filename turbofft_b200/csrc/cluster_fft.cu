@@ -10,7 +10,7 @@
 namespace tfft {
 
 namespace {
-typedef std::tuple<int, int, int, int> CKey;  // dtype, logn, logg, prefetch
+typedef std::tuple<int, int, int, int> CKey;  // dtype, logn, logg, prefetch + 2 * variant
 std::map<CKey, ClusterKernel>& ctable() {
     static std::map<CKey, ClusterKernel> t;
     return t;
@@ -22,17 +22,17 @@ std::map<std::pair<int, int>, int>& cdefault() {  // (dtype, logn) -> first regi
 }  // namespace
 
 void register_cluster_kernel(const ClusterKernel& k) {
-    ctable()[CKey(k.dtype, k.logn, k.logg, k.prefetch)] = k;
-    if (!k.prefetch) cdefault().insert({{k.dtype, k.logn}, k.logg});
+    ctable()[CKey(k.dtype, k.logn, k.logg, k.prefetch + 2 * k.variant)] = k;
+    if (!k.prefetch && !k.variant) cdefault().insert({{k.dtype, k.logn}, k.logg});
 }
 
-const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg, int prefetch) {
+const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg, int flavour) {
     if (logg < 0) {
         auto d = cdefault().find({dtype, logn});
         if (d == cdefault().end()) return nullptr;
         logg = d->second;
     }
-    auto it = ctable().find(CKey(dtype, logn, logg, prefetch ? 1 : 0));
+    auto it = ctable().find(CKey(dtype, logn, logg, flavour));
     return it == ctable().end() ? nullptr : &it->second;
 }
 
@@ -109,14 +109,15 @@ int cluster_kernel_fits(const ClusterKernel& k) {
 
 }  // namespace tfft
 
-#define TFFT_CLUSTER_INST_PF(T, DT, LOGN, LR0, LOGG, PF)                                                       \
-    template __global__ void tfft::cluster_fft_kernel<T, LOGN, LR0, LOGG, PF>(const __grid_constant__ tfft::ClusterArgs<T>); \
+#define TFFT_CLUSTER_INST_X(T, DT, LOGN, LR0, LOGG, PF, LRU)                                                   \
+    template __global__ void tfft::cluster_fft_kernel<T, LOGN, LR0, LOGG, PF, LRU>(                            \
+        const __grid_constant__ tfft::ClusterArgs<T>);                                                         \
     namespace {                                                                                                \
     struct TFFT_CAT(TfftClReg_, __LINE__) {                                                                    \
         TFFT_CAT(TfftClReg_, __LINE__)() {                                                                     \
-            typedef tfft::ClusterCfg<T, LOGN, LR0, LOGG> K;                                                    \
+            typedef tfft::ClusterCfg<T, LOGN, LR0, LOGG, LRU> K;                                               \
             tfft::ClusterKernel k;                                                                             \
-            k.fn = (const void*)&tfft::cluster_fft_kernel<T, LOGN, LR0, LOGG, PF>;                             \
+            k.fn = (const void*)&tfft::cluster_fft_kernel<T, LOGN, LR0, LOGG, PF, LRU>;                        \
             k.dtype = DT;                                                                                      \
             k.logn = LOGN;                                                                                     \
             k.lr0 = LR0;                                                                                       \
@@ -124,12 +125,14 @@ int cluster_kernel_fits(const ClusterKernel& k) {
             k.logg = LOGG;                                                                                     \
             k.s2 = K::S2;                                                                                      \
             k.prefetch = PF ? 1 : 0;                                                                           \
+            k.variant = (sizeof(T) == 4 && LRU == 3) ? 1 : 0;                                                  \
             k.threads = K::TH;                                                                                 \
             k.smem = PF ? K::SMEM_BYTES_PF : K::SMEM_BYTES;                                                    \
             tfft::register_cluster_kernel(k);                                                                  \
         }                                                                                                      \
     } TFFT_CAT(tfft_clreg_, __LINE__);                                                                         \
     }
+#define TFFT_CLUSTER_INST_PF(T, DT, LOGN, LR0, LOGG, PF) TFFT_CLUSTER_INST_X(T, DT, LOGN, LR0, LOGG, PF, (sizeof(T) == 4 ? 4 : 3))
 #define TFFT_CLUSTER_INST(T, DT, LOGN, LR0, LOGG) TFFT_CLUSTER_INST_PF(T, DT, LOGN, LR0, LOGG, false)
 #define TFFT_CAT2(a, b) a##b
 #define TFFT_CAT(a, b) TFFT_CAT2(a, b)
@@ -161,3 +164,9 @@ TFFT_CLUSTER_INST_PF(float, 0, 13, 1, 1, true)
 TFFT_CLUSTER_INST_PF(float, 0, 14, 2, 2, true)
 TFFT_CLUSTER_INST_PF(float, 0, 15, 3, 3, true)
 TFFT_CLUSTER_INST_PF(float, 0, 16, 4, 4, true)
+// complex64 with 8 units per thread (radix-8 unit stages): half the registers, twice the warps
+TFFT_CLUSTER_INST_X(float, 0, 13, 4, 1, false, 3)
+TFFT_CLUSTER_INST_X(float, 0, 14, 2, 2, false, 3)
+TFFT_CLUSTER_INST_X(float, 0, 15, 3, 3, false, 3)
+TFFT_CLUSTER_INST_X(float, 0, 16, 4, 4, false, 3)
+TFFT_CLUSTER_INST_X(float, 0, 15, 3, 4, false, 3)

@@ -91,9 +91,12 @@ __device__ __forceinline__ void dif_level_u(Unit<T> (&v)[R]) {
 }
 
 // ---------------------------------------------------------------- geometry
-template <typename T, int LOGN, int LR0, int LOGG>
+// LRU: log2 radix of the unit stages (a thread holds 2R complex points): 4 for complex64 at 128
+// registers per thread, 3 for complex128 -- and for the complex64 variant with half the registers
+// and twice the resident warps.
+template <typename T, int LOGN, int LR0, int LOGG, int LRU = (sizeof(T) == 4 ? 4 : 3)>
 struct ClusterCfg {
-    static constexpr int LR = sizeof(T) == 4 ? 4 : 3;  // radix of the unit stages: 2R complex points per thread
+    static constexpr int LR = LRU;
     static constexpr int R = 1 << LR, R0 = 1 << LR0;
     static constexpr int E = 2 * R;  // complex points per thread
     static constexpr int S2 = (LOGN - LR0) / LR;
@@ -124,9 +127,9 @@ struct ClusterCfg {
     static __host__ __device__ constexpr size_t twp_count(int t) { return ((size_t)LR << (LOGT - logp(t))) * 4; }  // in T
 };
 
-template <typename T, int LOGN, int LR0, int LOGG, bool PF = false>
+template <typename T, int LOGN, int LR0, int LOGG, bool PF = false, int LRU = (sizeof(T) == 4 ? 4 : 3)>
 struct ClusterFft {
-    typedef ClusterCfg<T, LOGN, LR0, LOGG> K;
+    typedef ClusterCfg<T, LOGN, LR0, LOGG, LRU> K;
     typedef typename Cplx<T>::type C;  // one complex value, or one value per lane
     typedef Unit<T> U;
     static constexpr int R = K::R, LR = K::LR, E = K::E, TH = K::TH, LOGT = K::LOGT;
@@ -449,11 +452,17 @@ struct ClusterFft {
     }
 };
 
-template <typename T, int LOGN, int LR0, int LOGG, bool PF>
-__global__ void __launch_bounds__((ClusterCfg<T, LOGN, LR0, LOGG>::TH), (PF ? 384 : 512) / ClusterCfg<T, LOGN, LR0, LOGG>::TH)
+// resident threads per SM the register cap aims at: 512 at 128 registers (384 with the landing
+// buffer of the prefetching variant), 1024 for the complex64 variant with 8 units per thread
+template <typename T, bool PF, int LRU>
+constexpr int cluster_resident_threads() { return (sizeof(T) == 4 && LRU == 3) ? 1024 : (PF ? 384 : 512); }
+
+template <typename T, int LOGN, int LR0, int LOGG, bool PF, int LRU>
+__global__ void __launch_bounds__((ClusterCfg<T, LOGN, LR0, LOGG, LRU>::TH),
+                                  (cluster_resident_threads<T, PF, LRU>() / ClusterCfg<T, LOGN, LR0, LOGG, LRU>::TH))
 cluster_fft_kernel(const __grid_constant__ ClusterArgs<T> a) {
     extern __shared__ __align__(16) unsigned char tfft_cluster_smem[];
-    ClusterFft<T, LOGN, LR0, LOGG, PF>::run(a, reinterpret_cast<T*>(tfft_cluster_smem));
+    ClusterFft<T, LOGN, LR0, LOGG, PF, LRU>::run(a, reinterpret_cast<T*>(tfft_cluster_smem));
 }
 
 }  // namespace tfft

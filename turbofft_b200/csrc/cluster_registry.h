@@ -30,6 +30,7 @@ struct ClusterArgs {
 struct ClusterKernel {
     const void* fn = nullptr;
     int dtype = 0, logn = 0, lr0 = 0, lr = 0, logg = 0, s2 = 0;
+    int variant = 0;   // complex64 only: 1 = 8 units per thread (radix-8 unit stages) instead of 16
     int prefetch = 0;  // 1: the next signal's input is fetched into shared memory by bulk copies while this one is transformed
     int threads = 0;
     size_t smem = 0;
@@ -37,7 +38,8 @@ struct ClusterKernel {
 
 void register_cluster_kernel(const ClusterKernel& k);
 // logg < 0: the first registered cluster size for (dtype, logn)
-const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg, int prefetch);
+// flavour = prefetch + 2 * variant
+const ClusterKernel* find_cluster_kernel(int dtype, int logn, int logg, int flavour);
 int registered_cluster_kernel_count();
 
 // Host images of the kernel's twiddle tables (ClusterArgs::tw0 / twp), as raw element arrays of
