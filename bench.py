@@ -54,6 +54,9 @@ def parse_args():
     ap.add_argument("--cufft", action="store_true", help="also time cuFFT on the same buffers (comparison only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--single-pass", type=int, default=None,
+                    help="sizes with a single-pass (cluster) kernel use it, with 2^(value & 15) CTAs per cluster "
+                         "(-1 = default size; +16 prefetching variant, +32 radix-8 variant); for profiling and comparison")
     ap.add_argument("--param-csv", default=None, help="plans from this parameter file instead of the built-in tables")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary measurements of the 'also' object")
     ap.add_argument("--also-steps", type=int, default=3)
@@ -455,6 +458,13 @@ def run_ours(a):
 
     plans = {}
     for logn in points:
+        if a.single_pass is not None and not a.ft:
+            try:
+                plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, thread_bs=a.thread_bs, device=local,
+                                      single_pass=a.single_pass)
+                continue
+            except tf.TurboFFTError:
+                pass  # no single-pass kernel of that size or cluster size: the launches
         plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2),
                               thread_bs=a.thread_bs, device=local, param_csv=a.param_csv)
     stream = torch.cuda.current_stream().cuda_stream
