@@ -508,7 +508,8 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
 #endif
     if (status == TFFT_OK && p->if_ft) {
         p->ft_count = (unsigned int*)dev_alloc(p, 6 * sizeof(unsigned int));
-        if (!p->ft_count) status = TFFT_ERR_ALLOC;
+        // zeroed here as well as before every exec: in accumulating mode nothing else clears them
+        if (!p->ft_count || !cuda_ok(p, cudaMemset(p->ft_count, 0, 6 * sizeof(unsigned int)))) status = TFFT_ERR_ALLOC;
         for (int i = 0; i < p->n_launch && status == TFFT_OK; ++i) {
             p->L[i].ft_located = (int*)dev_alloc(p, (size_t)p->L[i].grid * sizeof(int));
             p->L[i].ft_diag = dev_alloc(p, (size_t)p->L[i].grid * 3 * (p->esize() / 2));
@@ -897,6 +898,12 @@ int tfft_ft_status(tfft_plan p, int* n_detected, int* n_corrected, int launch, i
 
 int tfft_set_ft_accumulate(tfft_plan p, int enable) {
     if (!p) return TFFT_ERR_BAD_ARG;
+    if (enable && !p->ft_accumulate && p->ft_count) {  // start the totals from zero
+        DeviceGuard guard(p->device);
+        if (!guard.ok) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamSynchronize(p->last_stream)) || !cuda_ok(p, cudaMemset(p->ft_count, 0, 6 * sizeof(unsigned int))))
+            return TFFT_ERR_CUDA;
+    }
     p->ft_accumulate = enable ? 1 : 0;
     return TFFT_OK;
 }
