@@ -245,6 +245,30 @@ def test_strided_batch_along_a_middle_axis(torch_cuda, shape, dim, dtype):
     assert orc.rel_l2(back, x) <= 2 * orc.tolerance(CD[dtype], logn)
 
 
+def test_host_buffers_through_strided_and_single_pass_plans(torch_cuda):
+    """tfft_exec_host with plans that are not made of ordinary launches over whole signals: the
+    chunked pipeline does not apply, the call stages the whole array and runs the plan's own kernel."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    rng = np.random.default_rng(13)
+    x = (rng.standard_normal((40, 256, 4096)) + 1j * rng.standard_normal((40, 256, 4096))).astype(np.complex64)  # 320 MiB
+    xd = torch.from_numpy(x[:1]).cuda()
+    tf.fft(xd, dim=1)
+    plan = next(v for k, v in tf._plan_cache.items() if k[0] == "strided")
+    big = tf.Plan.__new__(tf.Plan)
+    import ctypes as C
+    big._h = C.c_void_p()
+    big.logN, big.batch, big.dtype, big.device, big.if_ft, big.if_err, big.thread_bs = 8, 40 * 4096, 0, 0, 0, 0, 1
+    assert tf.lib().tfft_plan_create_strided(C.byref(big._h), 8, 4096, 40, 0, 0) == 0
+    y = big.exec_host(torch.from_numpy(x).reshape(40 * 4096, 256)).numpy().reshape(40, 256, 4096)
+    assert orc.rel_l2(y[::13], np.fft.fft(x[::13].astype(np.complex128), axis=1)) <= orc.tolerance(np.complex64, 8)
+    xs = orc.make_input(4096, 1 << 15, np.complex64, seed=2)                                                   # 1 GiB
+    sp = tf.Plan(15, 4096, 0, single_pass=-1)
+    ys = sp.exec_host(torch.from_numpy(xs)).numpy()
+    assert orc.rel_l2(ys[::511], orc.fft_forward(xs[::511])) <= orc.tolerance(np.complex64, 15)
+
+
 def test_two_dimensional_transform(torch_cuda):
     import turbofft_b200 as tf
 

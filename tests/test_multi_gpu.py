@@ -280,7 +280,11 @@ def _gpu_worker(rank, world, port, logn, dtype, q):
         xg = torch.from_numpy(x[b:e].copy()).cuda()
         yf = fused(xg).cpu().numpy()
         yf2 = fused(xg).cpu().numpy()
+        # natural order, calls back to back with NO host synchronisation in between: the copy-out of
+        # call k reads the receive buffer that every peer's call k + 1 stores into first
+        back = [fused(xg) for _ in range(4)]
         torch.cuda.synchronize()
+        yf2 = max((t.cpu().numpy() for t in back), key=lambda a: orc.rel_l2(a, ref))
         dist.barrier()
         fused.close()
         # and with each exchange cut into pieces that overlap the local transforms

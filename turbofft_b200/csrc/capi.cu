@@ -683,7 +683,9 @@ int tfft_exec_ws(tfft_plan p, const void* in, void* out, void* workspace, void* 
 static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host, cudaStream_t user) {
     const size_t sig_bytes = ((size_t)1 << p->logn) * p->esize();
     long long cb = (long long)(kPipeChunkBytes / sig_bytes);
-    if (p->if_ft || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
+    // chunk plans are ordinary launch plans over whole signals: strided-batch and single-pass plans
+    // (and FT plans, whose status is per plan) take the unchunked path with their own kernels
+    if (p->if_ft || p->strided || p->ck || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
     if (!p->pipe_ready) {
         // every resource is created only if it is still missing, so a call that failed half way
         // can be repeated; the plan's destructor releases whatever exists

@@ -19,6 +19,12 @@
 // into the owning CTA's memory and fenced by barrier.cluster -- and all others stay inside the
 // CTA.  Global loads and stores are coalesced runs of at least 128 bytes per CTA.
 //
+// Variants of the one template: units per thread (16 at 128 registers; 8 -- radix-8 stages, one
+// stage more -- at 64 registers and twice the resident warps), cluster size (1 .. 16 CTAs), and a
+// prefetching form whose CTAs fetch their share of the next signal into a second shared-memory
+// buffer with cp.async.bulk copies completing on an mbarrier (bounded wait, status word) while the
+// current signal is transformed.
+//
 // Unit m of the Stockham array of a stage is read by global thread s = m mod T as its j-th
 // input, j = m / T (T = threads in the cluster); it lives in CTA rank(s) at local index
 // j * TH + lid(s), padded by pad(L) = L + (L >> 3) + (L >> 6) against bank conflicts.
