@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--datatype", type=int, default=0, help="0 float2 (complex64), 1 double2 (complex128)")
     ap.add_argument("--ft", type=int, default=0, help="0 off, 1 detect (--if_ft), 2 inject+correct (--if_err)")
-    ap.add_argument("--thread_bs", type=int, default=1)
+    ap.add_argument("--thread_bs", type=int, default=0, help="tiles per block; 0 = the tuned value of each size (param/B200/thread_bs_*.csv)")
     ap.add_argument("--lo", type=int, default=7)
     ap.add_argument("--hi", type=int, default=24)
     ap.add_argument("--log-total", type=int, default=28)
@@ -112,7 +112,7 @@ def make_host_input(n_complex, datatype, seed):
 def config_of(a):
     """The workload description both arms print (identical, so the two lines compare like for like)."""
     n, esize = 1 << a.log_total, 8 if a.datatype == 0 else 16
-    return {"workload": workload_name(a), "thread_bs": a.thread_bs,
+    return {"workload": workload_name(a), "thread_bs": a.thread_bs if a.thread_bs else "per size, the tuned table (1 except 2^14: 8)",
             "l2": f"inputs larger than L2 ({int(n * esize) >> 20} MiB per point vs {L2_BYTES >> 20} MiB)",
             "sharding": "batch sharded, each GPU its own 2^%d elements per point, no collective" % a.log_total}
 
@@ -315,7 +315,7 @@ def also_single_gpu(a, torch, tf, dev, x, y, stream, points, ours_ms, ours_per, 
                                              for l, o in zip(points, ours_per)}
     also["cufft"] = cu
     ft = {"thread_bs": "per size, the tuned table (plans created with thread_bs = 0)",
-          "baseline": "the headline sweep (FT off, thread_bs %d)" % a.thread_bs}
+          "baseline": "the headline sweep (FT off)"}
     for name, if_err in (("detect", 0), ("inject_correct", 1)):
         plans = {l: tf.Plan(l, 1 << (lt - l), a.datatype, if_ft=1, if_err=if_err, thread_bs=0, device=dev.index) for l in points}
         ms, per = time_sweep(torch, plans, points, x, y, stream, steps)
@@ -460,7 +460,7 @@ def run_ours(a):
     for logn in points:
         if a.single_pass is not None and not a.ft:
             try:
-                plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, thread_bs=a.thread_bs, device=local,
+                plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, thread_bs=max(1, a.thread_bs), device=local,
                                       single_pass=a.single_pass)
                 continue
             except tf.TurboFFTError:

@@ -37,6 +37,9 @@
 #ifndef TFFT_F32X2
 #define TFFT_F32X2 1  // complex64 butterflies add and subtract with the packed f32x2 instructions of sm_100
 #endif
+#ifndef TFFT_L2_PREFETCH
+#define TFFT_L2_PREFETCH 1  // blocks that loop over tiles ask L2 for the next tile while they transform this one
+#endif
 #ifndef TFFT_BOUNDS_CHECK
 #define TFFT_BOUNDS_CHECK 0  // 1: every global load/store index of the data buffers is checked (see KernelArgs::oob)
 #endif
@@ -520,6 +523,31 @@ struct Fft {
         }
     }
 
+    // Asks L2 for the input of a tile this block will load next (prefetch.global.L2, no register,
+    // no shared memory): the HBM read of tile t + 1 then overlaps the transform of tile t, which a
+    // block that fills its SM alone cannot get from a neighbour.  One request per 128-byte line.
+    static __device__ __forceinline__ void prefetch_tile(const KernelArgs<T>& a, long long tile_id) {
+#if TFFT_L2_PREFETCH
+        // only where a block fills its SM alone (whole signals of 128 KB and more): with several
+        // blocks per SM the neighbours already overlap their phases and the extra requests measured
+        // slower (2^12, 2^13 and every strided-line launch)
+        if constexpr (ROLE == ROLE_SINGLE && !K::STAGED_IO && K::SMEM_BYTES >= 120 * 1024) {
+            const Geom g = decode(a, tile_id);
+            int s, c;
+            map_thread<K::CFAST_IN>(s, c);
+            constexpr int PER_LINE = 128 / (2 * (int)sizeof(T));  // elements per 128-byte line
+            // the index that runs over adjacent addresses: the column for strided lines, the row otherwise
+            const int fast = K::CFAST_IN ? c : s;
+            if ((fast & (PER_LINE - 1)) == 0 && c < g.ncols) {
+                const C* src = a.in + g.in_base + (long long)c * g.in_cs + (long long)s * g.in_rs;
+#pragma unroll
+                for (int i = 0; i < E; ++i)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (long long)i * TPL * g.in_rs));
+            }
+        }
+#endif
+    }
+
     // One tile: load, all stages, store.  tin/tout receive this thread's share of the
     // tile's left and right checksums.
     template <bool DO_FT, bool DO_INJ, int CS = 0>
@@ -598,6 +626,7 @@ struct Fft {
             for (int it = 0; it < a.tiles_per_cta; ++it) {
                 const long long t = blockIdx.x + it * grid;
                 if (t >= a.n_tiles) break;
+                if (it + 1 < a.tiles_per_cta && t + grid < a.n_tiles) prefetch_tile(a, t + grid);
                 tile<false, false>(a, sm, t, false, f, tin, tout);
             }
             return;
@@ -635,6 +664,7 @@ struct Fft {
             const long long t = blockIdx.x + it * grid;
             if (t >= a.n_tiles) break;
             A tin2 = acc_zero<A>(), tout2 = acc_zero<A>();
+            if (it + 1 < a.tiles_per_cta && t + grid < a.n_tiles) prefetch_tile(a, t + grid);
             tile<true, true, CSACC>(a, sm, t, hit && it == inj_it, f, tin2, tout2);
             const T tin = acc_sum(tin2), tout = acc_sum(tout2);
             acc_in += tin;
