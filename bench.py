@@ -336,7 +336,7 @@ def also_single_gpu(a, torch, tf, dev, x, y, stream, points, ours_ms, ours_per, 
     else:
         xo = torch.view_as_complex(torch.rand(n, 2, generator=g, device=dev, dtype=rd) * 2 - 1)
     yo = torch.empty_like(xo)
-    plans = {l: tf.Plan(l, 1 << (lt - l), other, device=dev.index) for l in points}
+    plans = {l: tf.Plan(l, 1 << (lt - l), other, thread_bs=a.thread_bs, device=dev.index) for l in points}
     ms, per = time_sweep(torch, plans, points, xo, yo, stream, steps)
     gbs = 2.0 * n * es * len(points) / (ms * 1e-3) / 1e9
     rec = {"workload": ("cfg3" if other == 1 else "cfg2") + " sweep, " + ("complex128 N(0,1)" if other == 1 else "complex64 uniform[-1,1)"),
