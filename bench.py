@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--single-pass", type=int, default=None,
                     help="sizes with a single-pass (cluster) kernel use it, with 2^(value & 15) CTAs per cluster "
                          "(-1 = default size; +16 prefetching variant, +32 radix-8 variant); for profiling and comparison")
+    ap.add_argument("--fuse-launches", type=int, default=None, metavar="LOG_CHUNK_BYTES",
+                    help="two-launch sizes with a fused kernel run as ONE persistent kernel with chunks of 2^value bytes "
+                         "(tfft_plan_fuse_launches, lag 1); for profiling and comparison")
     ap.add_argument("--param-csv", default=None, help="plans from this parameter file instead of the built-in tables")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary measurements of the 'also' object")
     ap.add_argument("--also-steps", type=int, default=3)
@@ -467,6 +470,11 @@ def run_ours(a):
                 pass  # no single-pass kernel of that size or cluster size: the launches
         plans[logn] = tf.Plan(logn, 1 << (a.log_total - logn), a.datatype, if_ft=int(a.ft >= 1), if_err=int(a.ft == 2),
                               thread_bs=a.thread_bs, device=local, param_csv=a.param_csv)
+        if a.fuse_launches is not None and not a.ft:
+            try:
+                plans[logn].fuse_launches(max(0, a.fuse_launches - logn - (3 if a.datatype == 0 else 4)), 1)
+            except tf.TurboFFTError:
+                pass  # not a two-launch plan, or no fused kernel of its two launch shapes
     stream = torch.cuda.current_stream().cuda_stream
 
     def step(events=None):

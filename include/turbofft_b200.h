@@ -84,6 +84,17 @@ int tfft_plan_device_status(tfft_plan plan, int* status);
  * build), else TFFT_ERR_UNSUPPORTED.  FT off.  in == out is allowed.  tfft_set_direction
  * applies. */
 int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long long outer, int dtype, int device);
+/* Turns a two-launch plan (FT off) into ONE persistent, cooperatively launched kernel that runs
+ * both launches chunk by chunk: 2^log_chunk_signals signals per chunk, the last launch `lag`
+ * (0..2) chunks behind the first, the intermediate in a ring of 4 chunks that is small enough to
+ * stay in L2 -- the whole-batch intermediate of the two launches (2 * batch * N elements of HBM
+ * traffic) disappears and its buffer is freed.  Blocks order their accesses to the ring through
+ * per-chunk counters with bounded waits; tfft_plan_device_status reports 1 if a wait ever gave
+ * up (the output of that exec is then invalid).  TFFT_ERR_UNSUPPORTED if the plan is not two
+ * FT-off launches, no fused kernel is compiled for its two launch shapes, or the device cannot
+ * launch cooperatively.  The reference has no counterpart (its plans are separate launches,
+ * TurboFFT.h:120-140). */
+int tfft_plan_fuse_launches(tfft_plan plan, int log_chunk_signals, int lag);
 /* CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches. */
 int tfft_plan_cluster_size(tfft_plan plan);
 

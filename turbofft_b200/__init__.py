@@ -54,6 +54,17 @@ class Plan:
                                     self.thread_bs, param_csv.encode() if param_csv else None, self.device)
         _lib.check(rc, f"tfft_plan_create(logN={logN}, batch={batch}, dtype={dtype}, ft={if_ft}, err={if_err})")
 
+    def fuse_launches(self, log_chunk_signals: int, lag: int = 1) -> None:
+        """Run both launches of a two-launch plan as one persistent kernel whose intermediate stays in
+        L2 (tfft_plan_fuse_launches); raises if the plan or the device does not allow it."""
+        _lib.check(lib().tfft_plan_fuse_launches(self._h, int(log_chunk_signals), int(lag)), "tfft_plan_fuse_launches", self._h)
+
+    def device_status(self) -> int:
+        """1 if a bounded device-side wait of this plan's kernel ever gave up, else 0 (synchronises)."""
+        st = C.c_int(0)
+        _lib.check(lib().tfft_plan_device_status(self._h, C.byref(st)), "tfft_plan_device_status", self._h)
+        return st.value
+
     @property
     def cluster_size(self) -> int:
         """CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches."""

@@ -25,6 +25,7 @@ SIGNATURES = {
                                    C.c_char_p, C.c_int]),
     "tfft_plan_create_single_pass": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int]),
     "tfft_plan_cluster_size": (C.c_int, [C.c_void_p]),
+    "tfft_plan_fuse_launches": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "tfft_plan_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "tfft_plan_create_strided": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_longlong, C.c_longlong, C.c_int, C.c_int]),
     "tfft_exec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -95,7 +95,7 @@ def build_all(verbose: bool = True, jobs: int | None = None, with_cli: bool = Tr
     jobs = jobs or max(1, os.cpu_count() or 1)
     run_codegen(verbose)
     gen = sorted(glob.glob(os.path.join(CSRC, "generated", "*", "inst_*.cu")))
-    core = [os.path.join(CSRC, f) for f in ("capi.cu", "aux_kernels.cu", "cluster_fft.cu", "multi_gpu.cu", "registry.cpp", "params.cpp")]
+    core = [os.path.join(CSRC, f) for f in ("capi.cu", "aux_kernels.cu", "cluster_fft.cu", "pair_fft.cu", "multi_gpu.cu", "registry.cpp", "params.cpp")]
     objs, changed = _objects(core + gen, jobs, verbose)
     if changed or not os.path.exists(LIB):
         cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -27,6 +27,8 @@
 #include "params.h"
 #include "registry.h"
 #include "cluster_registry.h"
+#include "pair_fft.cuh"
+#include "pair_registry.h"
 
 using namespace tfft;
 
@@ -105,6 +107,13 @@ struct tfft_plan_s {
     void* ctwp[4] = {nullptr, nullptr, nullptr, nullptr};
     unsigned cgrid_clusters = 0;
     int* cstatus = nullptr;  // prefetching single-pass kernels: device word, 1 = a bounded wait gave up
+    // fused two-launch plan (one persistent kernel, intermediate in a ring that stays in L2)
+    const PairKernel* pk = nullptr;
+    void* ring = nullptr;
+    unsigned int* pair_done = nullptr;  // [2 * pair_chunks]
+    int* pair_status = nullptr;
+    long long pair_chunks = 0;
+    int pair_log_chunk = 0, pair_lag = 1, pair_ring_chunks = 4, pair_grid = 0;
     void* scratch = nullptr;
     void* scratch2 = nullptr;          // 3-launch plans that correct: the middle launch writes here, so that
                                        // its own input survives for the recompute of a located tile
@@ -333,9 +342,63 @@ int launch_cluster(tfft_plan p, const void* in, void* out, cudaStream_t st) {
 }
 
 template <typename T>
+void fill_launch_args(tfft_plan p, int i, KernelArgs<T>& a) {
+    typedef typename Cplx<T>::type C;
+    const LaunchDesc& d = p->L[i];
+    memset(&a, 0, sizeof(a));
+    a.tw_st = (const C*)d.tw_st;
+    a.tw_lo = (const C*)d.tw_lo;
+    a.tw_hi = (const C*)d.tw_hi;
+    a.cks = (const C*)d.cks;
+    a.n_tiles = d.n_tiles;
+    a.n_lines = d.n_lines;
+    a.tiles_per_cta = p->thread_bs;
+    a.log_n = p->logn;
+    a.log_b = d.log_b;
+    a.log_n1 = d.log_n1;
+    a.log_q = d.log_q;
+    a.tw_lo_bits = d.tw_lo_bits;
+    a.no_twiddle = p->strided;
+    a.conj_in = (p->inverse && i == 0) ? 1 : 0;
+    a.scale_out = ((p->inverse || p->scale != 1.0) && i == p->n_launch - 1) ? 1 : 0;
+    a.scale_x = (T)p->scale;
+    a.scale_y = (T)(p->inverse ? -p->scale : p->scale);
+    a.n_elems = p->batch << p->logn;
+    a.oob = p->oob;
+}
+
+// Both launches of a two-launch plan as one persistent kernel (pair_fft.cuh)
+template <typename T>
+int launch_pair(tfft_plan p, const void* in, void* out, cudaStream_t st) {
+    typedef typename Cplx<T>::type C;
+    PairArgs<T> a;
+    fill_launch_args<T>(p, 0, a.first);
+    fill_launch_args<T>(p, 1, a.last);
+    const long long ring_signals = (long long)p->pair_ring_chunks << p->pair_log_chunk;
+    a.first.in = (const C*)in;
+    a.first.out = (C*)p->ring;
+    a.last.in = (const C*)p->ring;
+    a.last.out = (C*)out;
+    a.first.ring_clear = a.last.ring_clear = ~(ring_signals - 1);
+    a.done = p->pair_done;
+    a.status = p->pair_status;
+    a.n_chunks = p->pair_chunks;
+    a.tiles1 = (int)((p->L[0].n_tiles / p->batch) << p->pair_log_chunk);
+    a.tiles2 = (int)((p->L[1].n_tiles / p->batch) << p->pair_log_chunk);
+    a.lag = p->pair_lag;
+    a.ring_chunks = p->pair_ring_chunks;
+    if (!cuda_ok(p, cudaMemsetAsync(p->pair_done, 0, (size_t)(2 * p->pair_chunks) * sizeof(unsigned int), st)))
+        return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, launch_pair_kernel(*p->pk, &a, p->pair_grid, st))) return TFFT_ERR_CUDA;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return TFFT_OK;
+}
+
+template <typename T>
 int launch_all(tfft_plan p, const void* in, void* out, cudaStream_t st, void* scratch) {
     typedef typename Cplx<T>::type C;
     if (p->ck) return launch_cluster<T>(p, in, out, st);
+    if (p->pk) return launch_pair<T>(p, in, out, st);
     const int ftmode = p->if_ft ? (p->if_err ? FT_CORRECT : FT_DETECT) : FT_OFF;
     if (p->if_ft && !p->ft_accumulate) {
         if (!cuda_ok(p, cudaMemsetAsync(p->ft_count, 0, 6 * sizeof(unsigned int), st))) return TFFT_ERR_CUDA;
@@ -639,10 +702,59 @@ int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long lo
 int tfft_plan_device_status(tfft_plan p, int* status) {
     if (!p || !status) return TFFT_ERR_BAD_ARG;
     *status = 0;
-    if (!p->cstatus) return TFFT_OK;
+    const int* word = p->cstatus ? p->cstatus : p->pair_status;
+    if (!word) return TFFT_OK;
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
-    if (!cuda_ok(p, cudaMemcpy(status, p->cstatus, sizeof(int), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaMemcpy(status, word, sizeof(int), cudaMemcpyDeviceToHost))) return TFFT_ERR_CUDA;
+    return TFFT_OK;
+}
+
+int tfft_plan_fuse_launches(tfft_plan p, int log_chunk_signals, int lag) {
+    if (!p || log_chunk_signals < 0 || log_chunk_signals > 20 || lag < 0 || lag > 2) return TFFT_ERR_BAD_ARG;
+    if (p->pk) return TFFT_OK;
+    if (p->n_launch != 2 || p->if_ft || p->strided || p->ck) return TFFT_ERR_UNSUPPORTED;
+    const LaunchDesc& a = p->L[0];
+    const LaunchDesc& b = p->L[1];
+    const PairKernel* pk = find_pair_kernel(p->dtype, a.logm, a.loge, a.logc, b.logm, b.loge, b.logc);
+    if (!pk) return TFFT_ERR_UNSUPPORTED;
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    int coop = 0;
+    if (!cuda_ok(p, cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, p->device))) return TFFT_ERR_CUDA;
+    const int resident = coop ? pair_kernel_resident_blocks(*pk) : 0;
+    if (resident < 1) return TFFT_ERR_UNSUPPORTED;
+    const long long chunk = 1LL << log_chunk_signals;
+    const long long chunks = (p->batch + chunk - 1) / chunk;
+    const long long t1 = (a.n_tiles / p->batch) << log_chunk_signals, t2 = (b.n_tiles / p->batch) << log_chunk_signals;
+    if (t1 > (1LL << 30) || t2 > (1LL << 30)) return TFFT_ERR_TOO_LARGE;
+    const int ring_chunks = 4;  // a power of two above lag + 1
+    void* ring = dev_alloc(p, ((size_t)(ring_chunks * chunk) << p->logn) * p->esize());
+    unsigned int* done = (unsigned int*)dev_alloc(p, (size_t)(2 * chunks) * sizeof(unsigned int));
+    int* status = (int*)dev_alloc(p, sizeof(int));
+    if (!ring || !done || !status) return TFFT_ERR_ALLOC;  // the plan keeps what was allocated until it is destroyed
+    if (!cuda_ok(p, cudaMemset(status, 0, sizeof(int)))) return TFFT_ERR_CUDA;
+    // the launches' whole-batch intermediate is not needed any more
+    if (p->scratch) {
+        for (size_t i = 0; i < p->allocs.size(); ++i)
+            if (p->allocs[i] == p->scratch) {
+                p->allocs.erase(p->allocs.begin() + (long)i);
+                break;
+            }
+        cudaFree(p->scratch);
+        p->owned_bytes -= ((size_t)p->batch << p->logn) * p->esize();
+        p->scratch = nullptr;
+    }
+    p->ring = ring;
+    p->pair_done = done;
+    p->pair_status = status;
+    p->pair_chunks = chunks;
+    p->pair_log_chunk = log_chunk_signals;
+    p->pair_lag = lag;
+    p->pair_ring_chunks = ring_chunks;
+    const long long items = (chunks + lag) * (t1 + t2);
+    p->pair_grid = (int)(items < resident ? items : resident);
+    p->pk = pk;
     return TFFT_OK;
 }
 

@@ -91,6 +91,9 @@ struct KernelArgs {
     // the element index); the offending access is skipped.  Unused in the normal build.
     long long n_elems;
     unsigned long long* oob;
+    // Fused two-launch kernel (pair_fft.cuh): bits of the signal index that are cleared when the
+    // intermediate is addressed, so that it lives in a ring of a few signals; 0 = whole buffer
+    long long ring_clear;
     int* ft_located;          // per block: located tile iteration (1-based) or -1
     unsigned int* ft_count;   // [0] blocks that detected, [1] tiles recomputed
     T* ft_diag;               // per block: delta, S, delta_w (may be null)
@@ -362,7 +365,8 @@ struct Fft {
             const int ltpo = a.log_b - LOGC;  // log2 tiles per outer index
             const long long o = tile >> ltpo;
             const long long b0 = (tile & ((1LL << ltpo) - 1)) << LOGC;
-            g.in_base = g.out_base = (o << (LOGM + a.log_b)) + b0;
+            g.in_base = (o << (LOGM + a.log_b)) + b0;
+            g.out_base = ((o & ~a.ring_clear) << (LOGM + a.log_b)) + b0;
             g.in_rs = g.out_rs = 1LL << a.log_b;
             g.in_cs = g.out_cs = 1;
             g.ncols = K::C;
@@ -373,7 +377,7 @@ struct Fft {
             const long long t = tile & ((1LL << (lk + a.log_q)) - 1);
             const long long k10 = (t & ((1LL << lk) - 1)) << LOGC;
             const long long k2 = t >> lk;
-            g.in_base = (batch << a.log_n) + (((k10 << a.log_q) + k2) << LOGM);
+            g.in_base = ((batch & ~a.ring_clear) << a.log_n) + (((k10 << a.log_q) + k2) << LOGM);
             g.in_rs = 1;
             g.in_cs = 1LL << (a.log_q + LOGM);
             g.out_base = (batch << a.log_n) + k10 + (k2 << a.log_n1);
@@ -550,9 +554,14 @@ struct Fft {
 
     // One tile: load, all stages, store.  tin/tout receive this thread's share of the
     // tile's left and right checksums.
-    template <bool DO_FT, bool DO_INJ, int CS = 0>
+    // L2ONLY: the input is read past L1 (it was written by other blocks of the SAME launch)
+    // after_loads: called once the tile's global loads have been issued (pair_fft.cuh hangs a deferred signal there)
+    struct NoHook {
+        __device__ __forceinline__ void operator()() const {}
+    };
+    template <bool DO_FT, bool DO_INJ, int CS = 0, bool L2ONLY = false, typename Hook = NoHook>
     static __device__ __forceinline__ void tile(const KernelArgs<T>& a, C* sm, long long tile_id, bool inject,
-                                                const FtRegs& f, A& tin, A& tout) {
+                                                const FtRegs& f, A& tin, A& tout, Hook after_loads = Hook()) {
         static_assert(CS == 0 || (!K::STAGED_IO && ROLE != ROLE_FIRST), "checksum correction: single and last launches only");
         const Geom g = decode(a, tile_id);
         int s, c;
@@ -584,13 +593,15 @@ struct Fft {
             const C* src = a.in + i0;
 #pragma unroll
             for (int i = 0; i < E; ++i) {
-                if (in_range(a, i0 + (long long)i * TPL * g.in_rs, 2)) v[i] = src[(long long)i * TPL * g.in_rs];
+                if (in_range(a, i0 + (long long)i * TPL * g.in_rs, 2))
+                    v[i] = L2ONLY ? __ldcg(src + (long long)i * TPL * g.in_rs) : src[(long long)i * TPL * g.in_rs];
                 else v[i].x = v[i].y = T(0);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].x = v[i].y = T(0);
         }
+        after_loads();
         if (CS != 2 && a.conj_in) {  // inverse transform: F^-1(x) = conj(F(conj(x))) / N
 #pragma unroll
             for (int i = 0; i < E; ++i) v[i].y = -v[i].y;
