@@ -92,7 +92,8 @@ int tfft_plan_create_strided(tfft_plan* plan, int logN, long long inner, long lo
  * per-chunk counters with bounded waits; tfft_plan_device_status reports 1 if a wait ever gave
  * up (the output of that exec is then invalid).  TFFT_ERR_UNSUPPORTED if the plan is not two
  * FT-off launches, no fused kernel is compiled for its two launch shapes, or the device cannot
- * launch cooperatively.  The reference has no counterpart (its plans are separate launches,
+ * launch cooperatively.  The ring and the counters belong to the plan: one exec at a time
+ * (tfft_exec_ws refuses such a plan).  The reference has no counterpart (its plans are separate launches,
  * TurboFFT.h:120-140). */
 int tfft_plan_fuse_launches(tfft_plan plan, int log_chunk_signals, int lag);
 /* CTAs per cluster of a single-pass plan, 0 for a plan made of ordinary launches. */
@@ -112,8 +113,8 @@ int tfft_exec(tfft_plan plan, const void* in, void* out, void* stream);
  * intermediate result of multi-launch plans in a buffer the plan owns, which two overlapping
  * execs would share).  workspace: tfft_scratch_bytes(plan) bytes of device memory, 256-byte
  * aligned, private to this exec until it has completed (NULL when that is 0: one-launch and
- * single-pass plans).  Plans without FT only (the FT status buffers are per plan):
- * TFFT_ERR_UNSUPPORTED otherwise.  The reference's launcher is single-threaded and
+ * single-pass plans).  Plans without FT only (the FT status buffers are per plan), and not
+ * fused plans (tfft_plan_fuse_launches): TFFT_ERR_UNSUPPORTED otherwise.  The reference's launcher is single-threaded and
  * synchronises after every launch (main.cu:58); it has nothing to share. */
 size_t tfft_scratch_bytes(tfft_plan plan);
 int tfft_exec_ws(tfft_plan plan, const void* in, void* out, void* workspace, void* stream);

@@ -772,13 +772,13 @@ int tfft_exec(tfft_plan p, const void* in, void* out, void* stream) {
 }
 
 size_t tfft_scratch_bytes(tfft_plan p) {
-    if (!p || p->n_launch < 2 || p->ck) return 0;
+    if (!p || p->n_launch < 2 || p->ck || p->pk) return 0;  // single-pass and fused plans carry what they need
     return ((size_t)p->batch << p->logn) * p->esize();
 }
 
 int tfft_exec_ws(tfft_plan p, const void* in, void* out, void* workspace, void* stream) {
     if (!p || !in || !out) return TFFT_ERR_BAD_ARG;
-    if (p->if_ft) return TFFT_ERR_UNSUPPORTED;  // the FT status buffers belong to the plan: one exec at a time
+    if (p->if_ft || p->pk) return TFFT_ERR_UNSUPPORTED;  // FT status buffers / the fused kernel's ring and counters belong to the plan: one exec at a time
     if (tfft_scratch_bytes(p) && !workspace) return TFFT_ERR_BAD_ARG;
     DeviceGuard guard(p->device);
     if (!guard.ok) return TFFT_ERR_CUDA;
@@ -797,7 +797,7 @@ static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host,
     long long cb = (long long)(kPipeChunkBytes / sig_bytes);
     // chunk plans are ordinary launch plans over whole signals: strided-batch and single-pass plans
     // (and FT plans, whose status is per plan) take the unchunked path with their own kernels
-    if (p->if_ft || p->strided || p->ck || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
+    if (p->if_ft || p->strided || p->ck || p->pk || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
     if (!p->pipe_ready) {
         // every resource is created only if it is still missing, so a call that failed half way
         // can be repeated; the plan's destructor releases whatever exists

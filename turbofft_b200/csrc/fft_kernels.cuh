@@ -37,14 +37,20 @@
 #ifndef TFFT_F32X2
 #define TFFT_F32X2 1  // complex64 butterflies add and subtract with the packed f32x2 instructions of sm_100
 #endif
+#ifndef TFFT_FT_PREFETCH
+#define TFFT_FT_PREFETCH 0  // 1: the FT kernels (eight tiles per block) prefetch as well; measured 3 % slower over the sweep
+#endif
 #ifndef TFFT_L2_PREFETCH
 #define TFFT_L2_PREFETCH 1  // blocks that loop over tiles ask L2 for the next tile while they transform this one
 #endif
 #ifndef TFFT_BOUNDS_CHECK
 #define TFFT_BOUNDS_CHECK 0  // 1: every global load/store index of the data buffers is checked (see KernelArgs::oob)
 #endif
+#ifndef TFFT_FT_LEAN
+#define TFFT_FT_LEAN 1  // 1: the FT kernels keep less state in registers (see FtRegs) and fit the plain kernels' 64
+#endif
 #ifndef TFFT_FT_OCC
-#define TFFT_FT_OCC 3  // quarters of the plain kernels' resident-thread target that the FT variants aim for
+#define TFFT_FT_OCC 4  // quarters of the plain kernels' resident-thread target that the FT variants aim for
 #endif
 
 namespace tfft {
@@ -275,8 +281,11 @@ struct Cfg {
     // The FT variants carry the checksum state on top and get a quarter more registers;
     // 32 points per thread need twice the registers, so half the threads.
     static constexpr int SMEM_BLOCKS = SMEM_BYTES ? (int)((220 * 1024) / SMEM_BYTES) : 32;
-    static constexpr int min_blocks(bool ft) {
-        const int target = (sizeof(T) == 4 ? 1024 : 512) * (ft ? TFFT_FT_OCC : 4) / 4 / (LOGE == 5 ? 2 : 1);
+    // ft: the FT mode (0 = off).  The complex64 detect / recompute kernels fit the plain kernels' register
+    // budget (TFFT_FT_OCC = 4 quarters); the running-checksum variant and complex128 spill there and keep 3.
+    static constexpr int min_blocks(int ft) {
+        const int quarters = ft == 0 ? 4 : ((sizeof(T) == 4 && ft != 3) ? TFFT_FT_OCC : 3);
+        const int target = (sizeof(T) == 4 ? 1024 : 512) * quarters / 4 / (LOGE == 5 ? 2 : 1);
         const int tb = (target + THREADS - 1) / THREADS;
         const int b = SMEM_BLOCKS < tb ? SMEM_BLOCKS : tb;
         return b < 1 ? 1 : b;
@@ -299,7 +308,11 @@ struct Fft {
     // weights are NOT kept here: 2E registers per thread cost more (spills or occupancy)
     // than re-reading them per tile from the L1-resident table.
     struct FtRegs {
+#if TFFT_FT_LEAN
+        int s3;   // s mod 3: which of the three fold weights the thread's first output takes
+#else
         C ab[3];  // fold weights (alpha, beta) of the right checksum, rotated by s mod 3
+#endif
     };
     typedef typename FtAcc<T>::type A;  // checksum accumulator of one tile
 
@@ -404,7 +417,29 @@ struct Fft {
         if (DO_FT) {
             constexpr int t3 = (K::LOGTPL & 1) ? 2 : 1;  // TPL mod 3
 #pragma unroll
+#if TFFT_FT_LEAN
+            // the outputs of each residue class are summed first (adds only), then the three sums are
+            // folded with the weights (1, 1), (a1, a2), (a2, a1), a1/a2 = -1/2 -/+ h, picked by s mod 3
+            C cls[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) cls[k].x = cls[k].y = T(0);
+#pragma unroll
+            for (int i = 0; i < E; ++i) cls[(i * t3) % 3] = cadd(cls[(i * t3) % 3], y[i]);
+            const T h = T(0.8660253882408142);
+            C w0, w1, w2;
+            w0.x = w0.y = T(1);
+            w1.x = T(-0.5) - h, w1.y = T(-0.5) + h;
+            w2.x = T(-0.5) + h, w2.y = T(-0.5) - h;
+            const int s3 = f.s3;  // class k carries weight (s3 + k) mod 3
+            const C c0 = s3 == 0 ? cls[0] : (s3 == 1 ? cls[2] : cls[1]);
+            const C c1 = s3 == 0 ? cls[1] : (s3 == 1 ? cls[0] : cls[2]);
+            const C c2 = s3 == 0 ? cls[2] : (s3 == 1 ? cls[1] : cls[0]);
+            acc_fma(tout, c0, w0);
+            acc_fma(tout, c1, w1);
+            acc_fma(tout, c2, w2);
+#else
             for (int i = 0; i < E; ++i) acc_fma(tout, y[i], f.ab[(i * t3) % 3]);
+#endif
         }
         if constexpr (CS != 0) {
             C* sy = sm + K::SMEM_ELEMS + E * K::THREADS + threadIdx.x;
@@ -535,7 +570,8 @@ struct Fft {
         // only where a block fills its SM alone (whole signals of 128 KB and more): with several
         // blocks per SM the neighbours already overlap their phases and the extra requests measured
         // slower (2^12, 2^13 and every strided-line launch)
-        if constexpr (ROLE == ROLE_SINGLE && !K::STAGED_IO && K::SMEM_BYTES >= 120 * 1024) {
+        if constexpr ((ROLE == ROLE_SINGLE && !K::STAGED_IO && K::SMEM_BYTES >= 120 * 1024) ||
+                      (TFFT_FT_PREFETCH && FT != FT_OFF && !K::STAGED_IO)) {
             const Geom g = decode(a, tile_id);
             int s, c;
             map_thread<K::CFAST_IN>(s, c);
@@ -653,12 +689,18 @@ struct Fft {
             const T alpha[3] = {T(1), T(-0.5) - h, T(-0.5) + h};
             const T beta[3] = {T(1), T(-0.5) + h, T(-0.5) - h};
             const int s3 = s % 3;
+#if TFFT_FT_LEAN
+            f.s3 = s3;
+            (void)alpha;
+            (void)beta;
+#else
 #pragma unroll
             for (int t = 0; t < 3; ++t) {
                 const int j = (s3 + t) % 3;
                 f.ab[t].x = j == 0 ? alpha[0] : (j == 1 ? alpha[1] : alpha[2]);
                 f.ab[t].y = j == 0 ? beta[0] : (j == 1 ? beta[1] : beta[2]);
             }
+#endif
         }
         const bool hit = a.inj_on && ((int)(blockIdx.x % (unsigned)a.inj_period) == a.inj_phase);
         const int inj_it = (int)((blockIdx.x / (unsigned)a.inj_period) % (unsigned)a.tiles_per_cta);
@@ -676,7 +718,7 @@ struct Fft {
             if (t >= a.n_tiles) break;
             A tin2 = acc_zero<A>(), tout2 = acc_zero<A>();
             if (it + 1 < a.tiles_per_cta && t + grid < a.n_tiles) prefetch_tile(a, t + grid);
-            tile<true, true, CSACC>(a, sm, t, hit && it == inj_it, f, tin2, tout2);
+            tile<true, !(TFFT_FT_LEAN && FT == FT_DETECT), CSACC>(a, sm, t, hit && it == inj_it, f, tin2, tout2);
             const T tin = acc_sum(tin2), tout = acc_sum(tout2);
             acc_in += tin;
             acc_out += tout;
@@ -741,7 +783,7 @@ struct Fft {
 
 template <typename T, int LOGM, int LOGE, int LOGC, int ROLE, int FT>
 __global__ void __launch_bounds__((Cfg<T, LOGM, LOGE, LOGC, ROLE>::THREADS),
-                                  (Cfg<T, LOGM, LOGE, LOGC, ROLE>::min_blocks(FT != FT_OFF)))
+                                  (Cfg<T, LOGM, LOGE, LOGC, ROLE>::min_blocks(FT)))
 fft_kernel(const __grid_constant__ KernelArgs<T> a) {
     extern __shared__ __align__(16) unsigned char tfft_smem_raw[];
     typedef typename Cplx<T>::type C;

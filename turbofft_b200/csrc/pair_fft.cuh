@@ -52,7 +52,7 @@ struct PairCfg {
     static_assert(K1::THREADS == K2::THREADS, "both launches must use the same block size");
     static constexpr int THREADS = K1::THREADS;
     static constexpr size_t SMEM_BYTES = K1::SMEM_BYTES > K2::SMEM_BYTES ? K1::SMEM_BYTES : K2::SMEM_BYTES;
-    static constexpr int MIN_BLOCKS = K1::min_blocks(false) < K2::min_blocks(false) ? K1::min_blocks(false) : K2::min_blocks(false);
+    static constexpr int MIN_BLOCKS = K1::min_blocks(FT_OFF) < K2::min_blocks(FT_OFF) ? K1::min_blocks(FT_OFF) : K2::min_blocks(FT_OFF);
 };
 
 // Publishes a finished tile: every store of the block that a barrier ordered before this call
