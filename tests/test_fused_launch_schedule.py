@@ -1,7 +1,8 @@
 """The ordering protocol of the fused two-launch kernel (csrc/pair_fft.cuh), replayed on the CPU.
 
-A persistent grid walks one work list ([first-launch tiles of chunk j][last-launch tiles of chunk
-j - lag] per super-step); the intermediate of chunk c lives in ring slot c mod R; two counters per
+A persistent grid draws tickets from one work list ([first-launch tiles of chunk j][last-launch
+tiles of chunk j - lag] per super-step; a block draws its next ticket while it works on the current
+one); the intermediate of chunk c lives in ring slot c mod R; two counters per
 chunk order the ring; a tile's signal is deferred into the block's next tile unless the block has
 to wait.  The model below mirrors the kernel's control flow step by step and lets a seeded
 adversarial scheduler pick which block moves next.  Checked for every interleaving tried:
@@ -18,11 +19,12 @@ R = 4  # ring chunks, as in tfft_plan_fuse_launches
 
 
 class Block:
-    def __init__(self, items):
-        self.items = items      # list of (is_first, chunk, local_tile)
-        self.pos = 0
+    def __init__(self):
+        self.item = None        # (is_first, chunk, local_tile) of the current ticket, None when the list is exhausted
+        self.next = None        # the ticket drawn ahead (an index into the list), None before the draw
         self.phase = "check"    # check -> (wait) -> load -> hook -> store
         self.pending = None     # counter key of the finished, unpublished tile
+        self.exhausted = False
 
 
 def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, grid, seed):
@@ -35,25 +37,44 @@ def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, gri
     def tiles_in(chunk, per, total):
         return min(per, total - chunk * per)
 
-    # the work list, exactly as the kernel decodes item i
+    # the work list, exactly as the kernel decodes item i (None: an empty slot, skipped with a fresh draw)
     per = t1 + t2
-    blocks = [Block([]) for _ in range(grid)]
+    items = []
     for i in range((n_chunks + lag) * per):
         j, slot = divmod(i, per)
         is_first = slot < t1
         chunk = j if is_first else j - lag
-        if chunk < 0 or chunk >= n_chunks:
-            continue
         local = slot if is_first else slot - t1
-        if chunk * (t1 if is_first else t2) + local >= (n_tiles1 if is_first else n_tiles2):
-            continue
-        blocks[i % grid].items.append((is_first, chunk, local))
+        if chunk < 0 or chunk >= n_chunks or chunk * (t1 if is_first else t2) + local >= (n_tiles1 if is_first else n_tiles2):
+            items.append(None)
+        else:
+            items.append((is_first, chunk, local))
+    queue = [0]
+
+    def draw():
+        queue[0] += 1
+        return queue[0] - 1
+
+    def take(b, ticket):
+        """The block starts the iteration of `ticket`: skips empty slots as the kernel does."""
+        while ticket < len(items) and items[ticket] is None:
+            ticket = draw()
+        if ticket >= len(items):
+            b.item, b.exhausted = None, True
+        else:
+            b.item = items[ticket]
+        b.next = None
+        b.phase = "check"
+
+    blocks = [Block() for _ in range(grid)]
+    for b in blocks:
+        take(b, draw())
 
     done = {}                                  # published counters: ("first"|"last", chunk) -> tiles
     stored = [dict() for _ in range(R)]        # ring slot -> {local first-launch tile: chunk}
     reads = {}                                 # chunk -> last-launch tiles that have read their slot
     finished = 0
-    total = sum(len(b.items) for b in blocks)
+    total = sum(1 for it in items if it is not None)
 
     def dependency(is_first, chunk):
         if is_first:
@@ -64,11 +85,11 @@ def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, gri
         return ("first", chunk), tiles_in(chunk, t1, n_tiles1)
 
     def runnable(b):
-        if b.pos >= len(b.items):
+        if b.exhausted:
             return b.pending is not None  # the final publish after the loop
         if b.phase != "wait":
             return True
-        key, need = dependency(*b.items[b.pos][:2])
+        key, need = dependency(*b.item[:2])
         return done.get(key, 0) >= need
 
     steps = 0
@@ -78,11 +99,11 @@ def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, gri
             break
         b = rng.choice(live)
         steps += 1
-        if b.pos >= len(b.items):
+        if b.exhausted:
             done[b.pending] = done.get(b.pending, 0) + 1
             b.pending = None
             continue
-        is_first, chunk, local = b.items[b.pos]
+        is_first, chunk, local = b.item
         dep = dependency(is_first, chunk)
         if b.phase == "check":
             if dep and done.get(dep[0], 0) < dep[1]:
@@ -105,6 +126,7 @@ def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, gri
             if b.pending is not None:
                 done[b.pending] = done.get(b.pending, 0) + 1
                 b.pending = None
+            b.next = draw()  # the next ticket is drawn while this tile runs
             b.phase = "store"
         else:
             if is_first:
@@ -113,9 +135,8 @@ def run_model(n_signals_tiles1, n_signals_tiles2, batch, chunk_signals, lag, gri
                     assert reads.get(prev, 0) == tiles_in(prev, t2, n_tiles2), "slot overwritten before it was read"
                 stored[chunk % R][local] = chunk
             b.pending = ("first" if is_first else "last", chunk)
-            b.pos += 1
-            b.phase = "check"
             finished += 1
+            take(b, b.next)
     assert finished == total, f"deadlock after {steps} steps: {finished} of {total} items"
     for c in range(n_chunks):
         assert done.get(("first", c), 0) == tiles_in(c, t1, n_tiles1)

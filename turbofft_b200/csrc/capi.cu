@@ -110,7 +110,7 @@ struct tfft_plan_s {
     // fused two-launch plan (one persistent kernel, intermediate in a ring that stays in L2)
     const PairKernel* pk = nullptr;
     void* ring = nullptr;
-    unsigned int* pair_done = nullptr;  // [2 * pair_chunks]
+    unsigned int* pair_done = nullptr;  // the ticket counter (8 bytes), then [2 * pair_chunks] tile counters
     int* pair_status = nullptr;
     long long pair_chunks = 0;
     int pair_log_chunk = 0, pair_lag = 1, pair_ring_chunks = 4, pair_grid = 0;
@@ -380,14 +380,15 @@ int launch_pair(tfft_plan p, const void* in, void* out, cudaStream_t st) {
     a.last.in = (const C*)p->ring;
     a.last.out = (C*)out;
     a.first.ring_clear = a.last.ring_clear = ~(ring_signals - 1);
-    a.done = p->pair_done;
+    a.queue = (unsigned long long*)p->pair_done;
+    a.done = p->pair_done + 2;
     a.status = p->pair_status;
     a.n_chunks = p->pair_chunks;
     a.tiles1 = (int)((p->L[0].n_tiles / p->batch) << p->pair_log_chunk);
     a.tiles2 = (int)((p->L[1].n_tiles / p->batch) << p->pair_log_chunk);
     a.lag = p->pair_lag;
     a.ring_chunks = p->pair_ring_chunks;
-    if (!cuda_ok(p, cudaMemsetAsync(p->pair_done, 0, (size_t)(2 * p->pair_chunks) * sizeof(unsigned int), st)))
+    if (!cuda_ok(p, cudaMemsetAsync(p->pair_done, 0, (size_t)(2 * p->pair_chunks + 2) * sizeof(unsigned int), st)))
         return TFFT_ERR_CUDA;
     if (!cuda_ok(p, launch_pair_kernel(*p->pk, &a, p->pair_grid, st))) return TFFT_ERR_CUDA;
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -730,7 +731,7 @@ int tfft_plan_fuse_launches(tfft_plan p, int log_chunk_signals, int lag) {
     if (t1 > (1LL << 30) || t2 > (1LL << 30)) return TFFT_ERR_TOO_LARGE;
     const int ring_chunks = 4;  // a power of two above lag + 1
     void* ring = dev_alloc(p, ((size_t)(ring_chunks * chunk) << p->logn) * p->esize());
-    unsigned int* done = (unsigned int*)dev_alloc(p, (size_t)(2 * chunks) * sizeof(unsigned int));
+    unsigned int* done = (unsigned int*)dev_alloc(p, (size_t)(2 * chunks + 2) * sizeof(unsigned int));
     int* status = (int*)dev_alloc(p, sizeof(int));
     if (!ring || !done || !status) return TFFT_ERR_ALLOC;  // the plan keeps what was allocated until it is destroyed
     if (!cuda_ok(p, cudaMemset(status, 0, sizeof(int)))) return TFFT_ERR_CUDA;
