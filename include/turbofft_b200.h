@@ -45,7 +45,8 @@ enum { TFFT_FLOAT2 = 0, TFFT_DOUBLE2 = 1 };
  * param_csv: path of an 11-column parameter file (logN, launches, logN1..3,
  * BS1..3, n1..3; readme.md:46-60) or NULL for the built-in B200 table.
  * if_ft / if_err / thread_bs: the reference CLI flags of the same names; thread_bs = 0 picks
- * the value the tuner recorded for this size (param/B200/thread_bs_<dtype>.csv, else 1).
+ * the value the tuner recorded for this size (param/B200/thread_bs_<dtype>.csv, else 1), cut down
+ * for small batches until every launch still has a block for every resident slot of the device.
  * Allocates the twiddle and checksum tables, the scratch buffer of multi-launch
  * plans and the FT status buffers on `device`. */
 int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int if_ft, int if_err,

@@ -313,3 +313,25 @@ def test_one_plan_on_two_streams_with_caller_workspaces(torch_cuda):
     assert all(torch.equal(y, w_) for y, w_ in zip(ys, want))
     ft = tf.Plan(logn, batch, 0, if_ft=1)
     assert lib.tfft_exec_ws(ft._h, xs[0].data_ptr(), ys[0].data_ptr(), ws[0].data_ptr(), 0) == -2
+
+
+def test_auto_thread_bs_shrinks_for_small_batches(torch_cuda):
+    """thread_bs = 0 takes the tuned value (32 tiles per block for 2^14-point complex64 signals, whose blocks fill an
+    SM each) only while the batch still gives every SM a block; the result is unaffected."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    big = tf.Plan(14, 64 * sms, tf.FLOAT2, thread_bs=0)
+    small = tf.Plan(14, 2 * sms, tf.FLOAT2, thread_bs=0)
+    tiny = tf.Plan(14, 3, tf.FLOAT2, thread_bs=0)
+    assert big.info()[0]["grid"] == 2 * sms        # 64 * sms tiles, 32 per block
+    assert small.info()[0]["grid"] == sms          # cut down to 2 per block
+    assert tiny.info()[0]["grid"] == 3             # one tile per block
+    x = torch.randn(2 * sms, 1 << 14, dtype=torch.complex64, device="cuda")
+    want = torch.fft.fft(x.to(torch.complex128), dim=1)
+    got = small(x)
+    rel = (torch.linalg.vector_norm(got.to(torch.complex128) - want) / torch.linalg.vector_norm(want)).item()
+    assert rel <= 1e-6 * 14, rel
+    for p in (big, small, tiny):
+        p.destroy()

@@ -468,7 +468,8 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
         return TFFT_ERR_BAD_ARG;
     NvtxRange range("tfft_plan_create");
     if (if_err) if_ft = 1;  // as the reference CLI does (CommandLineParser.h:62-64)
-    if (thread_bs == 0) thread_bs = builtin_thread_bs(dtype, logN, if_ft);  // the tuned value of this size
+    const bool auto_thread_bs = thread_bs == 0;
+    if (auto_thread_bs) thread_bs = builtin_thread_bs(dtype, logN, if_ft);  // the tuned value of this size
     std::vector<ParamRow> rows;
     std::string err;
     if (param_csv && param_csv[0]) {
@@ -550,6 +551,29 @@ int tfft_plan_create(tfft_plan* plan, int logN, long long batch, int dtype, int 
             if (!cuda_ok(p, cudaFuncSetAttribute(d.k->fn[ftmode], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)d.k->smem)))
                 status = TFFT_ERR_CUDA;
+        }
+    }
+    if (status == TFFT_OK && auto_thread_bs && thread_bs > 1) {
+        // The tuned value assumes a batch that fills the device many times over.  With fewer tiles it would leave
+        // SMs without a block, so it is cut down until every launch has at least one block per resident slot.
+        int sms = 0;
+        long long cap = thread_bs;
+        if (cuda_ok(p, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device))) {
+            for (int i = 0; i < p->n_launch; ++i) {
+                int per_sm = 0;
+                if (!cuda_ok(p, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, p->L[i].k->fn[ftmode],
+                                                                               p->L[i].k->threads, p->L[i].k->smem)))
+                    break;
+                const long long slots = (long long)sms * (per_sm > 0 ? per_sm : 1);
+                const long long fit = p->L[i].n_tiles / slots;
+                if (fit < cap) cap = fit < 1 ? 1 : fit;
+            }
+        }
+        p->last_cuda_error = 0;  // an occupancy query that failed only means no cap
+        if (cap < thread_bs) {
+            thread_bs = (int)cap;
+            p->thread_bs = thread_bs;
+            for (int i = 0; i < p->n_launch; ++i) p->L[i].grid = (unsigned)((p->L[i].n_tiles + thread_bs - 1) / thread_bs);
         }
     }
     if (status == TFFT_OK) {
