@@ -124,12 +124,23 @@ int tfft_exec_ws(tfft_plan plan, const void* in, void* out, void* workspace, voi
  * tfft_exec and copies the result back, then synchronises.  Replaces the
  * cudaMemcpy pair around the launches in initializeData()/test_turbofft()
  * (initializeData.h:39, main.cu:72).  Plans without FT whose batch spans at least
- * three 64 MiB chunks are pipelined: chunks of whole signals are copied in,
+ * three chunks (64 MiB of whole signals, or one signal of up to 512 MiB) are pipelined: chunks of whole signals are copied in,
  * transformed and copied out on three internal streams so both PCIe directions
- * overlap the kernels (use pinned host buffers).  Device staging buffers are
- * grow-only per device, shared by all plans and kept until the library is
- * unloaded; calls are serialised. */
+ * overlap the kernels (use pinned host buffers).  Device staging buffers, the
+ * three streams and their events are per device, grow-only, shared by all plans
+ * and kept until the library is unloaded; calls are serialised. */
 int tfft_exec_host(tfft_plan plan, const void* in_host, void* out_host, void* stream);
+/* The same call without the final synchronisation, for a sequence of transforms (of one plan or
+ * of several): the chunks of consecutive calls share the device's three pipeline streams, so the
+ * copy-out of one call's last chunks overlaps the copy-in of the next call's first ones instead
+ * of each call filling and draining the pipeline alone (about 6 % of a 2 GiB call).  The host
+ * buffers must stay valid and untouched until tfft_host_sync(device) has returned; results are
+ * complete only then.  Work queued on `stream` before the call is waited for; nothing is queued
+ * on `stream` behind it.  Plans the pipeline does not take (FT, strided, single-pass, fused,
+ * batches under three chunks) run and complete inside the call as tfft_exec_host does.  A plan
+ * may be destroyed while its chunks are in flight: tfft_plan_destroy waits for them. */
+int tfft_exec_host_async(tfft_plan plan, const void* in_host, void* out_host, void* stream);
+int tfft_host_sync(int device);
 
 /* Bytes of device memory the plan owns (tables + scratch + status). */
 size_t tfft_workspace_bytes(tfft_plan plan);

@@ -335,3 +335,34 @@ def test_auto_thread_bs_shrinks_for_small_batches(torch_cuda):
     assert rel <= 1e-6 * 14, rel
     for p in (big, small, tiny):
         p.destroy()
+
+
+def test_async_host_calls_share_the_pipeline(torch_cuda):
+    """tfft_exec_host_async: several transforms (two plans, different sizes) are queued back to back on the
+    device's copy pipeline and complete at tfft_host_sync; every result equals the synchronous call's."""
+    import turbofft_b200 as tf
+
+    torch = torch_cuda
+    torch.manual_seed(11)
+    cases = [(12, 3 * 2048 + 5), (16, 3 * 128 + 1), (12, 3 * 2048 + 5)]  # batches of at least three 64 MiB chunks, ragged
+    plans, xs, want, got = [], [], [], []
+    for logn, batch in cases:
+        p = tf.Plan(logn, batch, tf.FLOAT2, thread_bs=0)
+        x = torch.randn(batch << logn, dtype=torch.complex64).pin_memory()
+        plans.append(p)
+        xs.append(x)
+        want.append(p.exec_host(x))
+        got.append(torch.zeros_like(x).pin_memory())
+    for p, x, y in zip(plans, xs, got):
+        p.exec_host_async(x, y)
+    tf.host_sync(0)
+    for w, y in zip(want, got):
+        assert torch.equal(torch.view_as_real(w), torch.view_as_real(y))
+    # a plan may go while its chunks are still queued: destroy waits for them
+    y2 = torch.zeros_like(xs[1]).pin_memory()
+    plans[1].exec_host_async(xs[1], y2)
+    plans[1].destroy()
+    tf.host_sync(0)
+    assert torch.equal(torch.view_as_real(want[1]), torch.view_as_real(y2))
+    plans[0].destroy()
+    plans[2].destroy()

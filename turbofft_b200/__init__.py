@@ -14,7 +14,7 @@ from typing import Optional
 from . import _lib
 from ._lib import TurboFFTError, lib
 
-__all__ = ["Plan", "fft", "ifft", "TurboFFTError", "lib", "stream_copy", "launch_count"]
+__all__ = ["Plan", "fft", "ifft", "TurboFFTError", "lib", "stream_copy", "launch_count", "host_sync"]
 
 FLOAT2, DOUBLE2 = 0, 1
 
@@ -77,6 +77,10 @@ class Plan:
     def exec_host_ptr(self, in_ptr: int, out_ptr: int, stream: int = 0) -> None:
         _lib.check(lib().tfft_exec_host(self._h, in_ptr, out_ptr, stream), "tfft_exec_host", self._h)
 
+    def exec_host_async_ptr(self, in_ptr: int, out_ptr: int, stream: int = 0) -> None:
+        """tfft_exec_host without the final synchronisation: results are complete after host_sync(device)."""
+        _lib.check(lib().tfft_exec_host_async(self._h, in_ptr, out_ptr, stream), "tfft_exec_host_async", self._h)
+
     def __call__(self, x, out=None):
         """x: CUDA tensor [batch, N] (or [N] when batch == 1) of the plan's dtype."""
         torch = _torch()
@@ -106,6 +110,19 @@ class Plan:
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream().cuda_stream
             self.exec_host_ptr(x.data_ptr(), out.data_ptr(), stream)
+        return out
+
+    def exec_host_async(self, x, out):
+        """exec_host without the final synchronisation, for a sequence of transforms whose chunks should keep
+        the copy pipeline full: x and out (CPU tensors, pinned) must stay alive and untouched until
+        turbofft_b200.host_sync(device) has returned."""
+        torch = _torch()
+        if x.is_cuda or out.is_cuda or _dtype_code(x.dtype) != self.dtype or x.numel() != self.batch << self.logN \
+                or out.dtype != x.dtype or out.numel() != x.numel() or not (x.is_contiguous() and out.is_contiguous()):
+            raise ValueError("tensors do not match the plan")
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self.exec_host_async_ptr(x.data_ptr(), out.data_ptr(), stream)
         return out
 
     # -- introspection
@@ -252,6 +269,11 @@ def fft2(x, norm=None, inverse: bool = False):
     """2-D transform over the last two axes: the strided-batch plan along the rows' axis, then the
     ordinary plan along the last axis (both lengths powers of two)."""
     return fft(fft(x, dim=-2, norm=norm, inverse=inverse), norm=norm, inverse=inverse)
+
+
+def host_sync(device: int = 0) -> None:
+    """Waits for every chunk queued by Plan.exec_host_async_ptr on this device (tfft_host_sync)."""
+    _lib.check(lib().tfft_host_sync(int(device)), "tfft_host_sync")
 
 
 def stream_copy(src, dst) -> None:

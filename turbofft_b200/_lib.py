@@ -32,6 +32,8 @@ SIGNATURES = {
     "tfft_scratch_bytes": (C.c_size_t, [C.c_void_p]),
     "tfft_exec_ws": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tfft_exec_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tfft_exec_host_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tfft_host_sync": (C.c_int, [C.c_int]),
     "tfft_workspace_bytes": (C.c_size_t, [C.c_void_p]),
     "tfft_plan_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "tfft_set_ft_params": (C.c_int, [C.c_void_p, C.c_double, C.c_double, C.c_double]),

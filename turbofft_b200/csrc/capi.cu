@@ -47,12 +47,22 @@ struct StagePair {
 std::mutex g_stage_mu;
 std::map<int, StagePair> g_stage;
 
-// Chunk-sized staging slots of the pipelined host path (3 in + 3 out per device).
+// The pipelined host path of a device: chunk-sized staging slots (3 in + 3 out), one stream each for
+// copy-in, transform and copy-out, and the events that order the slots.  Shared by all plans of the
+// device and kept until the library is unloaded, so that consecutive calls -- of one plan or of
+// several -- keep the pipeline full: the copy-out tail of one call overlaps the copy-in head of the next.
 constexpr size_t kPipeChunkBytes = 64u << 20;
 struct PipeSlots {
     void* in[3] = {nullptr, nullptr, nullptr};
     void* out[3] = {nullptr, nullptr, nullptr};
     size_t bytes = 0;
+    cudaStream_t stream[3] = {nullptr, nullptr, nullptr};  // copy-in, transform, copy-out
+    cudaEvent_t ev_in[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fft[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_out[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_start = nullptr;
+    unsigned long long seq = 0;  // chunks queued so far: chunk n uses slot n % 3
+    bool ready = false;
 };
 std::map<int, PipeSlots> g_pipe;
 
@@ -140,12 +150,7 @@ struct tfft_plan_s {
     tfft_plan chunk_plan = nullptr;
     tfft_plan tail_plan = nullptr;
     long long chunk_batch = 0;
-    bool pipe_ready = false;  // sub-plans, streams and events of the pipelined host path all exist
-    cudaStream_t pipe_stream[3] = {nullptr, nullptr, nullptr};
-    cudaEvent_t ev_in[3] = {nullptr, nullptr, nullptr};
-    cudaEvent_t ev_fft[3] = {nullptr, nullptr, nullptr};
-    cudaEvent_t ev_out[3] = {nullptr, nullptr, nullptr};
-    cudaEvent_t ev_start = nullptr;
+    bool pipe_ready = false;  // the sub-plans of the pipelined host path exist
     size_t esize() const { return dtype == TFFT_FLOAT2 ? sizeof(float2) : sizeof(double2); }
 };
 
@@ -817,10 +822,12 @@ int tfft_exec_ws(tfft_plan p, const void* in, void* out, void* workspace, void* 
 // stream, transformed on a second and copied out on a third, three slots deep, so the two
 // PCIe directions and the kernels overlap.  Returns TFFT_ERR_UNSUPPORTED when the plan does
 // not qualify (the caller then takes the plain path).
-static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host, cudaStream_t user) {
+static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host, cudaStream_t user, bool sync) {
     const size_t sig_bytes = ((size_t)1 << p->logn) * p->esize();
     long long cb = (long long)(kPipeChunkBytes / sig_bytes);
-    // chunk plans are ordinary launch plans over whole signals: strided-batch and single-pass plans
+    // signals longer than a chunk travel one per chunk (up to 512 MiB each: six staging slots of that size)
+    if (cb < 1 && sig_bytes <= ((size_t)512 << 20)) cb = 1;
+    // chunk plans are ordinary launch plans over whole signals: strided-batch, single-pass and fused plans
     // (and FT plans, whose status is per plan) take the unchunked path with their own kernels
     if (p->if_ft || p->strided || p->ck || p->pk || cb < 1 || p->batch < 3 * cb) return TFFT_ERR_UNSUPPORTED;
     if (!p->pipe_ready) {
@@ -838,77 +845,79 @@ static int exec_host_pipelined(tfft_plan p, const void* in_host, void* out_host,
             if (rc != TFFT_OK) return rc;
         }
         tfft_set_direction(p, p->inverse, p->scale);  // hand the direction down to the sub-plans
-        for (int i = 0; i < 3; ++i) {
-            if (!p->pipe_stream[i] &&
-                !cuda_ok(p, cudaStreamCreateWithFlags(&p->pipe_stream[i], cudaStreamNonBlocking)))
-                return TFFT_ERR_CUDA;
-            if ((!p->ev_in[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming))) ||
-                (!p->ev_fft[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_fft[i], cudaEventDisableTiming))) ||
-                (!p->ev_out[i] && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_out[i], cudaEventDisableTiming))))
-                return TFFT_ERR_CUDA;
-        }
-        if (!p->ev_start && !cuda_ok(p, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming)))
-            return TFFT_ERR_CUDA;
         p->pipe_ready = true;
     }
     cb = p->chunk_batch;
     const size_t chunk_bytes = (size_t)cb * sig_bytes;
     std::lock_guard<std::mutex> lock(g_stage_mu);
     PipeSlots& ps = g_pipe[p->device];
+    if (!ps.ready) {
+        for (int i = 0; i < 3; ++i) {
+            if (!ps.stream[i] && !cuda_ok(p, cudaStreamCreateWithFlags(&ps.stream[i], cudaStreamNonBlocking)))
+                return TFFT_ERR_CUDA;
+            if ((!ps.ev_in[i] && !cuda_ok(p, cudaEventCreateWithFlags(&ps.ev_in[i], cudaEventDisableTiming))) ||
+                (!ps.ev_fft[i] && !cuda_ok(p, cudaEventCreateWithFlags(&ps.ev_fft[i], cudaEventDisableTiming))) ||
+                (!ps.ev_out[i] && !cuda_ok(p, cudaEventCreateWithFlags(&ps.ev_out[i], cudaEventDisableTiming))))
+                return TFFT_ERR_CUDA;
+        }
+        if (!ps.ev_start && !cuda_ok(p, cudaEventCreateWithFlags(&ps.ev_start, cudaEventDisableTiming)))
+            return TFFT_ERR_CUDA;
+        ps.ready = true;
+    }
+    cudaStream_t s_in = ps.stream[0], s_fft = ps.stream[1], s_out = ps.stream[2];
     if (ps.bytes < chunk_bytes) {
+        // larger slots: whatever earlier calls queued on the old ones has to finish first
+        for (int i = 0; i < 3; ++i)
+            if (!cuda_ok(p, cudaStreamSynchronize(ps.stream[i]))) return TFFT_ERR_CUDA;
         for (int i = 0; i < 3; ++i) {
             if (ps.in[i]) cudaFree(ps.in[i]);
             if (ps.out[i]) cudaFree(ps.out[i]);
             ps.in[i] = ps.out[i] = nullptr;
         }
         ps.bytes = 0;
+        ps.seq = 0;
         for (int i = 0; i < 3; ++i)
             if (!cuda_ok(p, cudaMalloc(&ps.in[i], chunk_bytes)) || !cuda_ok(p, cudaMalloc(&ps.out[i], chunk_bytes)))
                 return TFFT_ERR_ALLOC;
         ps.bytes = chunk_bytes;
     }
-    cudaStream_t s_in = p->pipe_stream[0], s_fft = p->pipe_stream[1], s_out = p->pipe_stream[2];
     // everything queued on the caller's stream so far comes first
-    if (!cuda_ok(p, cudaEventRecord(p->ev_start, user))) return TFFT_ERR_CUDA;
+    if (!cuda_ok(p, cudaEventRecord(ps.ev_start, user))) return TFFT_ERR_CUDA;
     for (int i = 0; i < 3; ++i)
-        if (!cuda_ok(p, cudaStreamWaitEvent(p->pipe_stream[i], p->ev_start, 0))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamWaitEvent(ps.stream[i], ps.ev_start, 0))) return TFFT_ERR_CUDA;
     const long long nchunk = (p->batch + cb - 1) / cb;
     for (long long c = 0; c < nchunk; ++c) {
-        const int slot = (int)(c % 3);
+        const int slot = (int)(ps.seq % 3);
         const long long this_b = (c == nchunk - 1 && p->batch % cb) ? p->batch % cb : cb;
         const size_t bytes = (size_t)this_b * sig_bytes;
         const char* src = (const char*)in_host + (size_t)c * chunk_bytes;
         char* dst = (char*)out_host + (size_t)c * chunk_bytes;
-        if (c >= 3) {
-            // slot reuse: its previous transform has consumed in[slot], its previous copy-out has drained out[slot]
-            if (!cuda_ok(p, cudaStreamWaitEvent(s_in, p->ev_fft[slot], 0))) return TFFT_ERR_CUDA;
-            if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, p->ev_out[slot], 0))) return TFFT_ERR_CUDA;
+        if (ps.seq >= 3) {
+            // slot reuse (by this call or an earlier one): its previous transform has consumed in[slot], its
+            // previous copy-out has drained out[slot]
+            if (!cuda_ok(p, cudaStreamWaitEvent(s_in, ps.ev_fft[slot], 0))) return TFFT_ERR_CUDA;
+            if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, ps.ev_out[slot], 0))) return TFFT_ERR_CUDA;
         }
+        ++ps.seq;
         if (!cuda_ok(p, cudaMemcpyAsync(ps.in[slot], src, bytes, cudaMemcpyHostToDevice, s_in))) return TFFT_ERR_CUDA;
-        if (!cuda_ok(p, cudaEventRecord(p->ev_in[slot], s_in))) return TFFT_ERR_CUDA;
-        if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, p->ev_in[slot], 0))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaEventRecord(ps.ev_in[slot], s_in))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamWaitEvent(s_fft, ps.ev_in[slot], 0))) return TFFT_ERR_CUDA;
         const int rc = tfft_exec(this_b == cb ? p->chunk_plan : p->tail_plan, ps.in[slot], ps.out[slot], s_fft);
         if (rc != TFFT_OK) return rc;
-        if (!cuda_ok(p, cudaEventRecord(p->ev_fft[slot], s_fft))) return TFFT_ERR_CUDA;
-        if (!cuda_ok(p, cudaStreamWaitEvent(s_out, p->ev_fft[slot], 0))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaEventRecord(ps.ev_fft[slot], s_fft))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaStreamWaitEvent(s_out, ps.ev_fft[slot], 0))) return TFFT_ERR_CUDA;
         if (!cuda_ok(p, cudaMemcpyAsync(dst, ps.out[slot], bytes, cudaMemcpyDeviceToHost, s_out))) return TFFT_ERR_CUDA;
-        if (!cuda_ok(p, cudaEventRecord(p->ev_out[slot], s_out))) return TFFT_ERR_CUDA;
+        if (!cuda_ok(p, cudaEventRecord(ps.ev_out[slot], s_out))) return TFFT_ERR_CUDA;
     }
-    for (int i = 0; i < 3; ++i)
-        if (!cuda_ok(p, cudaStreamSynchronize(p->pipe_stream[i]))) return TFFT_ERR_CUDA;
     p->last_stream = s_fft;
+    if (sync)
+        for (int i = 0; i < 3; ++i)
+            if (!cuda_ok(p, cudaStreamSynchronize(ps.stream[i]))) return TFFT_ERR_CUDA;
     return TFFT_OK;
 }
 
-int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* stream) {
-    if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
-    NvtxRange range("tfft_exec_host");
-    DeviceGuard guard(p->device);
-    if (!guard.ok) return TFFT_ERR_CUDA;
-    {
-        const int rc = exec_host_pipelined(p, in_host, out_host, (cudaStream_t)stream);
-        if (rc != TFFT_ERR_UNSUPPORTED) return rc;
-    }
+// the unchunked form: whole batch in, transform, whole batch out on the caller's stream
+static int exec_host_plain(tfft_plan p, const void* in_host, void* out_host, void* stream) {
     const size_t bytes = ((size_t)p->batch << p->logn) * p->esize();
     std::lock_guard<std::mutex> lock(g_stage_mu);
     StagePair& sp = g_stage[p->device];
@@ -929,6 +938,39 @@ int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* strea
     if (rc != TFFT_OK) return rc;
     if (!cuda_ok(p, cudaMemcpyAsync(out_host, sp.out, bytes, cudaMemcpyDeviceToHost, st))) return TFFT_ERR_CUDA;
     if (!cuda_ok(p, cudaStreamSynchronize(st))) return TFFT_ERR_CUDA;
+    return TFFT_OK;
+}
+
+int tfft_exec_host(tfft_plan p, const void* in_host, void* out_host, void* stream) {
+    if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
+    NvtxRange range("tfft_exec_host");
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    const int rc = exec_host_pipelined(p, in_host, out_host, (cudaStream_t)stream, true);
+    if (rc != TFFT_ERR_UNSUPPORTED) return rc;
+    return exec_host_plain(p, in_host, out_host, stream);
+}
+
+int tfft_exec_host_async(tfft_plan p, const void* in_host, void* out_host, void* stream) {
+    if (!p || !in_host || !out_host) return TFFT_ERR_BAD_ARG;
+    NvtxRange range("tfft_exec_host_async");
+    DeviceGuard guard(p->device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    const int rc = exec_host_pipelined(p, in_host, out_host, (cudaStream_t)stream, false);
+    if (rc != TFFT_ERR_UNSUPPORTED) return rc;
+    // plans the pipeline does not take run at once; what the pipeline still holds is unaffected
+    return exec_host_plain(p, in_host, out_host, stream);
+}
+
+int tfft_host_sync(int device) {
+    if (device < 0) return TFFT_ERR_BAD_ARG;
+    DeviceGuard guard(device);
+    if (!guard.ok) return TFFT_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_stage_mu);
+    auto it = g_pipe.find(device);
+    if (it == g_pipe.end()) return TFFT_OK;
+    for (int i = 0; i < 3; ++i)
+        if (it->second.stream[i] && cudaStreamSynchronize(it->second.stream[i]) != cudaSuccess) return TFFT_ERR_CUDA;
     return TFFT_OK;
 }
 
@@ -1101,15 +1143,9 @@ int tfft_ft_diag(tfft_plan p, int launch, double* diag, int cap_blocks) {
 int tfft_plan_destroy(tfft_plan p) {
     if (!p) return TFFT_ERR_BAD_ARG;
     DeviceGuard guard(p->device);
+    if (p->pipe_ready) tfft_host_sync(p->device);  // chunks this plan queued with tfft_exec_host_async still use its sub-plans
     if (p->chunk_plan) tfft_plan_destroy(p->chunk_plan);
     if (p->tail_plan) tfft_plan_destroy(p->tail_plan);
-    for (int i = 0; i < 3; ++i) {
-        if (p->pipe_stream[i]) cudaStreamDestroy(p->pipe_stream[i]);
-        if (p->ev_in[i]) cudaEventDestroy(p->ev_in[i]);
-        if (p->ev_fft[i]) cudaEventDestroy(p->ev_fft[i]);
-        if (p->ev_out[i]) cudaEventDestroy(p->ev_out[i]);
-    }
-    if (p->ev_start) cudaEventDestroy(p->ev_start);
     for (void* q : p->allocs) cudaFree(q);
     delete p;
     return TFFT_OK;
