@@ -316,7 +316,7 @@ def test_one_plan_on_two_streams_with_caller_workspaces(torch_cuda):
 
 
 def test_auto_thread_bs_shrinks_for_small_batches(torch_cuda):
-    """thread_bs = 0 takes the tuned value (32 tiles per block for 2^14-point complex64 signals, whose blocks fill an
+    """thread_bs = 0 takes the tuned value (8 tiles per block for 2^14-point complex64 signals, whose blocks fill an
     SM each) only while the batch still gives every SM a block; the result is unaffected."""
     import turbofft_b200 as tf
 
@@ -325,7 +325,7 @@ def test_auto_thread_bs_shrinks_for_small_batches(torch_cuda):
     big = tf.Plan(14, 64 * sms, tf.FLOAT2, thread_bs=0)
     small = tf.Plan(14, 2 * sms, tf.FLOAT2, thread_bs=0)
     tiny = tf.Plan(14, 3, tf.FLOAT2, thread_bs=0)
-    assert big.info()[0]["grid"] == 2 * sms        # 64 * sms tiles, 32 per block
+    assert big.info()[0]["grid"] == 8 * sms        # 64 * sms tiles, 8 per block
     assert small.info()[0]["grid"] == sms          # cut down to 2 per block
     assert tiny.info()[0]["grid"] == 3             # one tile per block
     x = torch.randn(2 * sms, 1 << 14, dtype=torch.complex64, device="cuda")
