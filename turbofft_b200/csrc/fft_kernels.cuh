@@ -416,7 +416,6 @@ struct Fft {
             for (int q = 0; q < R; ++q) y[u + q * NB] = v[u + brev<LR>(q) * NB];
         if (DO_FT) {
             constexpr int t3 = (K::LOGTPL & 1) ? 2 : 1;  // TPL mod 3
-#pragma unroll
 #if TFFT_FT_LEAN
             // the outputs of each residue class are summed first (adds only), then the three sums are
             // folded with the weights (1, 1), (a1, a2), (a2, a1), a1/a2 = -1/2 -/+ h, picked by s mod 3
@@ -438,6 +437,7 @@ struct Fft {
             acc_fma(tout, c1, w1);
             acc_fma(tout, c2, w2);
 #else
+#pragma unroll
             for (int i = 0; i < E; ++i) acc_fma(tout, y[i], f.ab[(i * t3) % 3]);
 #endif
         }
