@@ -207,7 +207,7 @@ def test_tuner_run_times_the_current_row(torch_cuda, tmp_path):
 
     out = tmp_path / "r.json"
     tune.main(["run", "--datatype", "float2", "--lo", "10", "--hi", "10", "--reps", "1", "--burn", "1", "--log-total", "20",
-               "--thread-bs", "1,4", "--out", str(out)])
+               "--thread-bs", "1,4", "--sustain-ms", "5", "--sweep-lo", "9", "--sweep-hi", "11", "--out", str(out)])
     res = json.loads(out.read_text())["10"]
     assert res["tried"] >= 1 and res["best"][0] > 0 and res["current_ms"] > 0
     assert set(res["thread_bs_ms"]) == {"0:1", "0:4", "1:1", "1:4"} and res["thread_bs"][0] in (1, 4)

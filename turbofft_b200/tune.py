@@ -20,6 +20,7 @@ import json
 import os
 import sys
 import tempfile
+import time
 
 from . import planner
 
@@ -110,7 +111,36 @@ def cmd_emit(a):
     print(f"wrote {n} candidate rows to {path}")
 
 
-def _time_plan(torch, plan, x, y, stream, burn, reps):
+class _Sweep:
+    """The built-in plans of the sizes lo..hi over the same buffers: run for a while before a candidate is
+    timed, they put the GPU into the state the sweep benchmark sees it in (sustained load, power-capped
+    clocks).  Rankings taken in short bursts on a cool GPU have turned over there more than once."""
+
+    def __init__(self, tf, lo, hi, log_total, dt):
+        self.plans = []
+        for logn in range(lo, hi + 1):
+            try:
+                self.plans.append(tf.Plan(logn, 1 << (log_total - logn), dt, thread_bs=0))
+            except tf.TurboFFTError:
+                pass
+
+    def heat(self, torch, x, y, stream, ms):
+        if ms <= 0 or not self.plans:
+            return
+        t0 = time.perf_counter()
+        while (time.perf_counter() - t0) * 1e3 < ms:
+            for p in self.plans:
+                p.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
+            torch.cuda.synchronize()
+
+    def destroy(self):
+        for p in self.plans:
+            p.destroy()
+
+
+def _time_plan(torch, plan, x, y, stream, burn, reps, sweep=None, sustain_ms=0):
+    if sweep is not None:
+        sweep.heat(torch, x, y, stream, sustain_ms)
     for _ in range(burn):
         plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -136,6 +166,7 @@ def cmd_run(a):
     stream = torch.cuda.current_stream().cuda_stream
     current = planner.load_params(a.datatype, a.gpu)
     results = {}
+    sweep = _Sweep(tf, a.sweep_lo, a.sweep_hi, a.log_total, dt) if a.sustain_ms > 0 else None
     for logn in range(a.lo, a.hi + 1):
         cands = [current[logn]] + candidates(logn, a.datatype)
         best = None
@@ -150,16 +181,7 @@ def cmd_run(a):
                 os.unlink(path)
                 continue
             os.unlink(path)
-            for _ in range(a.burn):   # --burn > 2 brings the GPU to its sustained, power-capped clocks first
-                plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            e0.record()
-            for _ in range(a.reps):
-                plan.exec_ptr(x.data_ptr(), y.data_ptr(), stream)
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / a.reps
+            ms = _time_plan(torch, plan, x, y, stream, a.burn, a.reps, sweep, a.sustain_ms)
             plan.destroy()
             rows.append((ms, row_text(r)))
             if best is None or ms < best[0]:
@@ -176,7 +198,7 @@ def cmd_run(a):
                     plan = tf.Plan(logn, 1 << (a.log_total - logn), dt, if_ft=ft, thread_bs=tbs, param_csv=path)
                 except tf.TurboFFTError:
                     continue
-                tbs_ms[f"{ft}:{tbs}"] = _time_plan(torch, plan, x, y, stream, a.burn, a.reps)
+                tbs_ms[f"{ft}:{tbs}"] = _time_plan(torch, plan, x, y, stream, a.burn, a.reps, sweep, a.sustain_ms)
                 plan.destroy()
         os.unlink(path)
         pick = {ft: min((v, int(k.split(":")[1])) for k, v in tbs_ms.items() if k.startswith(f"{ft}:"))[1]
@@ -186,6 +208,8 @@ def cmd_run(a):
                               "thread_bs": [pick.get(0, 1), pick.get(1, 1)]}
         print(f"logN {logn}: best {best[0]:.3f} ms [{best[1]}] current {results[str(logn)]['current_ms']} ({len(rows)} tried) "
               f"thread_bs FT off/on {results[str(logn)]['thread_bs']}", flush=True)
+    if sweep is not None:
+        sweep.destroy()
     with open(a.out, "w") as f:
         json.dump(results, f, indent=1)
 
@@ -232,6 +256,11 @@ def main(argv=None):
             p.add_argument("--log-total", type=int, default=28)
             p.add_argument("--reps", type=int, default=5)
             p.add_argument("--burn", type=int, default=2, help="untimed runs before the timed ones")
+            p.add_argument("--sustain-ms", type=float, default=0.0,
+                           help="run the built-in sweep (--sweep-lo..--sweep-hi) this long before every timing, so that "
+                                "candidates are ranked at the sustained, power-capped clocks the sweep benchmark runs at")
+            p.add_argument("--sweep-lo", type=int, default=7)
+            p.add_argument("--sweep-hi", type=int, default=24)
             p.add_argument("--out", default="tune_results.json")
             p.add_argument("--thread-bs", type=lambda t: [int(v) for v in t.split(",")], default=[1, 2, 4, 8],
                            help="thread_bs values tried for the winning row")
