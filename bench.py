@@ -62,7 +62,7 @@ def parse_args():
                          "(tfft_plan_fuse_launches, lag 1); for profiling and comparison")
     ap.add_argument("--param-csv", default=None, help="plans from this parameter file instead of the built-in tables")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary measurements of the 'also' object")
-    ap.add_argument("--also-steps", type=int, default=3)
+    ap.add_argument("--also-steps", type=int, default=5)
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-log-sample", type=int, default=28, help="log2 elements per sweep point in the CPU sample")
     ap.add_argument("--workload", default="sweep", choices=["sweep", "fourstep", "cfg1", "cfg4"],
@@ -115,7 +115,7 @@ def make_host_input(n_complex, datatype, seed):
 def config_of(a):
     """The workload description both arms print (identical, so the two lines compare like for like)."""
     n, esize = 1 << a.log_total, 8 if a.datatype == 0 else 16
-    return {"workload": workload_name(a), "thread_bs": a.thread_bs if a.thread_bs else "per size, the tuned table (1, except 8 for the SM-filling single launches 2^14 complex64 and 2^13 complex128)",
+    return {"workload": workload_name(a), "thread_bs": a.thread_bs if a.thread_bs else "per size, the tuned table (1, except 8 for the SM-filling single launch of 2^14 complex64)",
             "l2": f"inputs larger than L2 ({int(n * esize) >> 20} MiB per point vs {L2_BYTES >> 20} MiB)",
             "sharding": "batch sharded, each GPU its own 2^%d elements per point, no collective" % a.log_total}
 

@@ -39,7 +39,7 @@ def test_ft_detect_only_clean_input(torch_cuda, logn, batch, tbs, dtype):
 def last_launch_tiles(x, row):
     """Inputs of the last launch of a plan, as [tile][line][M], in tile order.
 
-    1 launch: tiles of C consecutive signals (zero padded).  2 launches: the first
+    1 launch: tiles of C consecutive signals (zero padded).  2 and 3 launches: the first
     launch's output inter[b, k1, n2] = FFT_n1(x[b, n1, n2]) * W_N^(n2 k1); a tile of the
     last launch is C consecutive k1 of one signal (csrc/fft_kernels.cuh, ROLE_LAST)."""
     ls = planner.launches_of_row(row)
@@ -51,14 +51,25 @@ def last_launch_tiles(x, row):
         xt = np.zeros((nt * C, M), np.complex128)
         xt[:batch] = x
         return xt.reshape(nt, C, M), l
-    assert len(ls) == 2
     n1 = 1 << ls[0].logm
     n2 = n // n1
     inter = np.fft.fft(x.astype(np.complex128).reshape(batch, n1, n2), axis=1)
     k1 = np.arange(n1)[:, None]
     c2 = np.arange(n2)[None, :]
     inter = inter * np.exp(-2j * np.pi * ((k1 * c2) % n) / n)
-    return inter.reshape(batch * n1 // C, C, n2), l
+    if len(ls) == 2:
+        return inter.reshape(batch * n1 // C, C, n2), l
+    # 3 launches: the middle launch transforms the middle digit of every (b, k1) row of length n2 = m2 * m3,
+    # B[b, k1, k2, n3] = FFT_m2(inter[b, k1, m2, n3]) * W_(m2 m3)^(n3 k2); a tile of the last launch is C
+    # consecutive k1 at one k2, tiles ordered signal, k2, k1 group (csrc/fft_kernels.cuh, ROLE_LAST with log_q)
+    assert len(ls) == 3
+    m2 = 1 << ls[1].logm
+    m3 = n2 // m2
+    mid = np.fft.fft(inter.reshape(batch, n1, m2, m3), axis=2)
+    k2 = np.arange(m2)[:, None]
+    c3 = np.arange(m3)[None, :]
+    mid = mid * np.exp(-2j * np.pi * ((k2 * c3) % n2) / n2)
+    return mid.transpose(0, 2, 1, 3).reshape(batch * m2 * n1 // C, C, m3), l
 
 
 @pytest.mark.parametrize("dtype", [0, 1])
